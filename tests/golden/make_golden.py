@@ -1,0 +1,70 @@
+"""Regenerates the golden vectors in this folder from the UNMODIFIED reference.
+
+Run where the reference tree is available (it is compiled, where it lies, by
+`make -C oracle ref`):   python tests/golden/make_golden.py
+
+Everything written here comes out of the reference's own Model::forward,
+Inference::generateTokens, Tensor::randomNormal and load_checkpoint_weights (through
+oracle/ref_shim.cpp); nothing is computed by this repository's code.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle.binding import Config, RefModel, build_ref, prompt_ids  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+SMALL = Config(vocab=512, context=64, layers=2, d_model=64, heads=2, ffn=96)
+SMALL_EOS_MERGES = 512 - 6 - 256          # Tokenizer::getEosToken() = 256 + merges = 506
+
+
+def sha(a: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def small():
+    r = RefModel(SMALL)
+    r.init_normal(0, 0.02)
+    w_sha = [sha(a) for _, a in r.params()]
+    names = [n for n, _ in r.params()]
+    r.init_normal(3, 0.2)                  # peaked logits: exercises top-p and the penalty
+    ids = prompt_ids(1, 2 * 24, SMALL.vocab)
+    logits = r.forward(ids, 2, 24)
+    prompt = prompt_ids(5, 8, SMALL.vocab)
+    streams = {}
+    for seed, (t, p, pen, n) in {2: (0.8, 0.95, 1.15, 100), 1234: (0.7, 0.8, 1.1, 40), 3: (0.7, 0.8, 1.1, 80)}.items():
+        streams[f"stream_seed{seed}"] = r.generate_tokens(prompt, n, t, p, pen, seed, eos_merges=SMALL_EOS_MERGES)
+        streams[f"opts_seed{seed}"] = np.array([t, p, pen, n], dtype=np.float64)
+    np.savez_compressed(os.path.join(OUT, "small_ref.npz"), ids=ids, logits=logits, prompt=prompt,
+                        weight_names=np.array(names), weight_sha_seed0=np.array(w_sha), **streams)
+
+
+def c1_probe():
+    """100.3M config, seed-0 N(0,0.02) weights, the first 24 ids of the seed-1 prompt."""
+    cfg = Config()
+    r = RefModel(cfg)
+    r.init_normal(0, 0.02)
+    T = 24
+    ids = prompt_ids(1, 128)[:T]
+    logits = r.forward(ids, 1, T)[0]                      # [T, V]
+    probe = prompt_ids(99, 512)                           # fixed probe columns
+    top = np.argsort(-logits, axis=1, kind="stable")[:, :8].astype(np.uint32)
+    emb = r.param(0)[1]
+    np.savez_compressed(os.path.join(OUT, "c1_ref_probe.npz"), ids=ids, probe_cols=probe,
+                        probe_logits=logits[:, probe], top_ids=top,
+                        top_vals=np.take_along_axis(logits, top.astype(np.int64), axis=1),
+                        row_absmax=np.abs(logits).max(axis=1), row_sum=logits.astype(np.float64).sum(axis=1),
+                        emb_row0=emb[0].copy(), emb_sha=np.array(sha(emb)),
+                        last_param_sha=np.array(sha(r.param(r.num_params() - 2)[1])))
+
+
+if __name__ == "__main__":
+    if build_ref() is None:
+        sys.exit("reference tree not available; golden vectors can only be regenerated where it is")
+    small()
+    c1_probe()
+    print("golden vectors written to", OUT)
