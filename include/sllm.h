@@ -1,0 +1,154 @@
+/* sllm.h -- C ABI of the B200 token-loop engine (libsllm_b200.so).
+ *
+ * This is the drop-in boundary for small-llm's generate/sample path: plain pointers and
+ * sizes, opaque handles, int status codes, no C++ or CUDA types.  Each entry point names the
+ * small-llm interface it stands in for (paths inside the small-llm tree).  The C++ classes
+ * with the reference's own names (ModelConfig, Model, Inference, SamplingOptions,
+ * load_checkpoint_weights) are a header-only layer over these calls: include/small_llm.hpp.
+ *
+ * Threading: an engine belongs to one host thread and one GPU.  Several engines (one per
+ * GPU, or several on one GPU) may live in one process.  There is no CPU fallback: every call
+ * that computes needs a CUDA device of compute capability 10.x and fails with
+ * SLLM_ERR_CUDA otherwise.
+ */
+#ifndef SLLM_H
+#define SLLM_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes; the C++ layer maps them back to the reference's exception types */
+enum {
+    SLLM_OK = 0,
+    SLLM_ERR_INVALID = 1,    /* std::invalid_argument: shapes, empty prompt, bad config      */
+    SLLM_ERR_IO = 2,         /* std::runtime_error: checkpoint cannot be opened / is corrupt  */
+    SLLM_ERR_CUDA = 3,       /* std::runtime_error: a CUDA call failed, or no usable device   */
+    SLLM_ERR_CAPACITY = 4,   /* std::runtime_error: batch slots or KV pages exhausted         */
+    SLLM_ERR_DEVICE_WAIT = 5,/* a bounded device-side wait gave up (status word set)          */
+    SLLM_ERR_NONFINITE = 6,  /* std::runtime_error: "all logits are non-finite"               */
+    SLLM_ERR_STATE = 7       /* std::logic_error: call made in the wrong state                */
+};
+
+/* ModelConfig, include/config.h:6-47 (same fields, same defaults when zero-initialised by
+ * sllm_default_model_config). */
+typedef struct {
+    uint64_t vocab_size, context_length, num_layers, d_model, num_heads, ffn_hidden;
+    float rope_theta;
+    float rms_eps;           /* ModelConfig::kRmsNormEps */
+} sllm_model_config;
+
+enum { SLLM_WEIGHTS_BF16 = 0, SLLM_WEIGHTS_F32 = 1 };
+
+typedef struct {
+    uint32_t max_batch;        /* sequences that can be live at once                          */
+    uint32_t weight_dtype;     /* SLLM_WEIGHTS_BF16: bf16 weights and KV cache, fp32 residual
+                                  stream and accumulation.  SLLM_WEIGHTS_F32: fp32 weights and
+                                  KV cache (parity runs that need the reference's streams)    */
+    uint64_t kv_pages;         /* pages of 64 positions in the pool; 0 = max_batch * ceil(ctx/64) */
+    uint32_t max_chunk_tokens; /* tokens one prefill pass may carry; 0 = default (8192)       */
+    int32_t device;            /* CUDA device ordinal; -1 = current                           */
+    uint32_t use_graph;        /* replay the decode step as a CUDA graph (1) or launch (0)    */
+    uint32_t reserved;
+} sllm_engine_options;
+
+/* SamplingOptions, include/inference.h:9-15, plus the EOS id that the reference takes from
+ * Tokenizer::getEosToken() (include/tokenizer.h:69). */
+typedef struct {
+    float temperature;         /* <= 0: greedy */
+    float top_p;
+    float repetition_penalty;  /* 1.0 = off */
+    uint32_t eos_token;
+    int64_t stop_token;        /* -1 = none */
+    uint64_t seed;             /* used only when no draws are supplied */
+} sllm_sampling;
+
+typedef struct sllm_engine sllm_engine;
+
+typedef struct {
+    uint64_t weight_bytes, kv_bytes, scratch_bytes;   /* device memory held               */
+    uint64_t kv_pages_total, kv_pages_free;
+    uint64_t launches;           /* kernels launched by this engine since creation (graph nodes counted per replay) */
+    uint64_t decode_steps;
+    float last_step_ms;          /* device time of the most recent sllm_decode_step         */
+} sllm_stats;
+
+void sllm_default_model_config(sllm_model_config* cfg);      /* include/config.h:15-46 defaults */
+void sllm_default_engine_options(sllm_engine_options* opt);
+void sllm_default_sampling(sllm_sampling* s);                /* include/inference.h:10-14, eos 32762 */
+
+/* Error text of the last failing call on this engine (engine may be NULL for create errors). */
+const char* sllm_last_error(const sllm_engine* e);
+
+/* Model::Model + Model::to(CUDA) + Model::enable_bf16, src/model.cpp:15-29,133-149: allocates
+ * every device buffer the engine will ever use (weights, KV page pool, scratch). Weights are
+ * zero (gains 1) until set. */
+int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* opt, sllm_engine** out);
+void sllm_engine_destroy(sllm_engine* e);
+int sllm_engine_stats(sllm_engine* e, sllm_stats* out);
+/* cudaStream_t of the engine (as void*), for callers that time with events. */
+void* sllm_engine_stream(sllm_engine* e);
+
+/* Model::parameters(), src/model.cpp:106-131: registry order and names. */
+uint32_t sllm_num_params(const sllm_engine* e);
+int sllm_param_info(const sllm_engine* e, uint32_t index, char name[64], uint64_t dims[2], uint32_t* ndim);
+/* Assigning *p.value followed by Model::refresh_bf16_weights(), src/model.cpp:151-158:
+ * host fp32 row-major data in the reference's shape; converted and re-laid-out on the device. */
+int sllm_set_param(sllm_engine* e, const char* name, const float* host_data, const uint64_t* dims, uint32_t ndim);
+/* load_checkpoint_weights, src/checkpoint.cpp:57-102: same file layout, same checks. */
+int sllm_load_checkpoint(sllm_engine* e, const char* path, uint64_t* step, uint64_t* data_position);
+
+/* Model::forward, src/model.cpp:31-62: B rows of T ids -> host logits [B,T,vocab] fp32.
+ * Uses sequence slots 0..B-1 (their previous contents are dropped). */
+int sllm_forward_logits(sllm_engine* e, const uint32_t* ids, uint64_t B, uint64_t T, float* host_logits);
+
+/* ---- the token loop, step by step (src/inference.cpp:39-160) ------------------------- */
+/* Drop every sequence and return all KV pages to the pool. */
+int sllm_reset(sllm_engine* e);
+/* Load prompts into slots 0..n_seq-1 (ids concatenated, lens[i] each >= 1), run them through
+ * the model, leave each slot's last-position logits in the step-logits buffer. */
+int sllm_prefill(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq);
+/* Sampler body, src/inference.cpp:101-160, for every live slot on the device: penalty over the
+ * slot's whole history, temperature softmax, top-p, draw, append, stop on EOS / stop token.
+ * draws: n_seq doubles in [0,1) in HOST memory, one per slot (NULL allowed when greedy). */
+int sllm_sample(sllm_engine* e, const sllm_sampling* opt, const double* draws);
+/* Model::forward for the one new token of every live slot (KV-cached): appends K/V, leaves
+ * new step logits. */
+int sllm_decode_step(sllm_engine* e);
+/* Copy a slot's step logits [vocab] to the host (what the reference reads at
+ * src/inference.cpp:57,73). */
+int sllm_get_step_logits(sllm_engine* e, uint32_t slot, float* host_logits);
+/* Replace a slot's step logits with caller-supplied ones (HOST memory, [vocab]); the next
+ * sllm_sample then works on them, as the reference's host sampler works on any logits row. */
+int sllm_set_step_logits(sllm_engine* e, uint32_t slot, const float* host_logits);
+/* Tokens of a slot so far (prompt + continuation); returns the count in *n. */
+int sllm_get_tokens(sllm_engine* e, uint32_t slot, uint32_t* host_out, uint64_t capacity, uint64_t* n);
+/* Overwrite the token that the next sllm_decode_step will feed to a slot (teacher forcing). */
+int sllm_force_token(sllm_engine* e, uint32_t slot, uint32_t token);
+/* Rewind a slot to its first n tokens (n >= 1, n <= current length): later positions are
+ * forgotten, step logits become stale until the next decode step. */
+int sllm_truncate(sllm_engine* e, uint32_t slot, uint64_t n_tokens);
+
+/* ---- the token loop in one call: Inference::generateTokens, src/inference.cpp:21-173 --- */
+/* All buffers are HOST memory.  prompts concatenated; out_tokens is [n_seq][out_stride] and
+ * receives prompt + continuation per slot, out_lens the counts.
+ * draws: [max_new][n_seq] doubles, draw[step][slot] feeds step `step` of that slot (indexed by
+ * step, not consumed sequentially); NULL = seeded mode, reproducing the reference's
+ * std::mt19937_64(seed) + std::discrete_distribution consumption (a draw is used only when at
+ * least two candidates are kept) with slot s using seed + s.
+ * A slot stops after EOS or stop_token is appended, after max_new tokens, or when its length
+ * reaches context_length (sliding the window is left to the caller, see small_llm.hpp). */
+int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* prompt_lens, uint32_t n_seq,
+                  uint64_t max_new_tokens, const sllm_sampling* opt, const double* draws,
+                  uint32_t* out_tokens, uint64_t out_stride, uint64_t* out_lens);
+
+/* Device-resident variant used by benchmarks: the decode loop only, for slots already
+ * prefilled; runs n_steps x (sample, decode step) without host round trips and returns after
+ * the stream is idle.  draws_dev_index selects how draws are consumed as in sllm_generate. */
+int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLLM_H */

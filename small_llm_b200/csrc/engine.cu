@@ -1,0 +1,1056 @@
+// Host engine + C ABI (include/sllm.h) of the B200 token loop.
+//
+// One engine = one GPU, one stream, every device buffer allocated at creation:
+//   weights     re-laid-out at load time (repack.cuh)
+//   KV pool     [L][pages][2][H][64][hd], pages handed to slots by the host (block table on device)
+//   slot state  tokens, lengths, finished flags, seen-id bitmaps, draw cursors
+//   pass state  token list (id, slot, position) of the pass in flight + activations
+// A "pass" runs the model over a list of new tokens; a prefill pass carries a chunk of prompt
+// tokens, a decode pass one token per slot.  The decode iteration (sampler + pass) is replayed
+// as a CUDA graph with programmatic dependent launches between its kernels.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <random>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../../include/sllm.h"
+#include "attn_decode.cuh"
+#include "common.cuh"
+#include "gemv.cuh"
+#include "repack.cuh"
+#include "sampler.cuh"
+
+using namespace sllm;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+struct ParamSlot {
+    std::string name;
+    uint64_t dims[2];
+    uint32_t ndim;
+    int kind;    // 0 embedding, 1 attn_norm, 2 q, 3 k, 4 v, 5 out, 6 ffn_norm, 7 gate, 8 up, 9 down, 10 final_norm
+    int layer;
+};
+
+struct GraphKey {
+    int n_slots; float t, p, pen; uint32_t eos; long long stop; int seeded; int stride; const void* draws;
+    bool operator<(const GraphKey& o) const {
+        return std::tie(n_slots, t, p, pen, eos, stop, seeded, stride, draws) <
+               std::tie(o.n_slots, o.t, o.p, o.pen, o.eos, o.stop, o.seeded, o.stride, o.draws);
+    }
+};
+
+}  // namespace
+
+struct sllm_engine {
+    sllm_model_config cfg{};
+    sllm_engine_options opt{};
+    ModelDims md{};
+    bool f32 = false;
+    int dev = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    std::string err;
+
+    // weights
+    std::vector<ParamSlot> params;
+    std::vector<LayerW> layers;
+    std::vector<void*> allocs;
+    void* emb_w = nullptr;        // [V][D] weight dtype (tied head)
+    float* emb_f32 = nullptr;     // [V][D] fp32 (gather)
+    float* g_final = nullptr;
+    float2* rope = nullptr;
+    float* staging = nullptr;     // largest parameter, fp32
+    size_t staging_elems = 0;
+    uint64_t weight_bytes = 0, kv_bytes = 0, scratch_bytes = 0;
+
+    // KV
+    void* kv_pool = nullptr;
+    long long n_pages = 0;
+    int pages_per_seq = 0;
+    std::vector<int> free_pages;
+    std::vector<std::vector<int>> slot_pages;
+    int* d_block_table = nullptr;
+
+    // slots
+    SeqState st{};
+    int max_batch = 0;
+    int n_live = 0;                    // slots 0..n_live-1 are in use
+    std::vector<int> h_len_bound;      // upper bound of each slot's token count (host view)
+
+    // pass buffers
+    int pass_cap = 0;                  // tokens per pass
+    uint32_t* d_tok_id = nullptr; int* d_tok_slot = nullptr; int* d_tok_pos = nullptr;
+    uint32_t* d_dec_id = nullptr; int* d_dec_slot = nullptr; int* d_dec_pos = nullptr;   // decode pass (written by the sampler)
+    float* x = nullptr; float* q = nullptr; float* att = nullptr; float* hid = nullptr;
+    int* d_row_tok = nullptr;
+    float* step_logits = nullptr;      // [max_batch][V]
+    float* pass_logits = nullptr;      // [logit_rows_cap][V]
+    int logit_rows_cap = 0;
+    // attention scratch
+    float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
+    int split_tok_cap = 64;
+    // draws
+    double* d_draws = nullptr; size_t draws_cap = 0;
+    // host pinned
+    int* h_flags = nullptr;
+
+    // graphs
+    std::map<GraphKey, cudaGraphExec_t> graphs;
+
+    uint64_t launches = 0, decode_steps = 0;
+    float last_step_ms = 0.f;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    size_t max_dyn_smem = 0;
+};
+
+namespace {
+
+#define CU(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t _e = (call);                                                                   \
+        if (_e != cudaSuccess) {                                                                   \
+            char _b[512];                                                                          \
+            std::snprintf(_b, sizeof _b, "CUDA error %s at %s:%d: %s", cudaGetErrorName(_e), __FILE__, __LINE__, \
+                          cudaGetErrorString(_e));                                                 \
+            e->err = _b;                                                                           \
+            return SLLM_ERR_CUDA;                                                                  \
+        }                                                                                          \
+    } while (0)
+
+int fail(sllm_engine* e, int code, const std::string& msg) {
+    if (e) e->err = msg; else g_create_error = msg;
+    return code;
+}
+
+template <typename T>
+int dalloc(sllm_engine* e, T** p, size_t count, uint64_t* counter) {
+    void* q = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 256);
+    CU(cudaMalloc(&q, bytes));
+    CU(cudaMemsetAsync(q, 0, bytes, e->stream));
+    e->allocs.push_back(q);
+    *p = static_cast<T*>(q);
+    if (counter) *counter += bytes;
+    return SLLM_OK;
+}
+
+size_t wsize(const sllm_engine* e) { return e->f32 ? 4 : 2; }
+
+// ---- launch helper: every kernel of the engine goes through here ---------------------------------
+template <typename... KArgs, typename... Args>
+int launch(sllm_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = e->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    CU(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
+    e->launches += 1;
+    return SLLM_OK;
+}
+
+// Dynamic shared memory above 48 KB is opted into once, at engine creation (configure_kernels).
+template <typename K>
+int set_smem(sllm_engine*, K, size_t) { return SLLM_OK; }
+
+template <typename K>
+int opt_in_smem(sllm_engine* e, K kern) {
+    CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->max_dyn_smem));
+    return SLLM_OK;
+}
+
+// ---- projections ---------------------------------------------------------------------------------------
+template <typename WT, int MODE>
+int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
+    const int groups = a.R / 2;
+    int gx = std::min((groups + kGemvWarps - 1) / kGemvWarps, e->sm_count * 4);
+    const int n = a.n_tok;
+    int nt = n == 1 ? 1 : (n == 2 ? 2 : (n <= 4 ? 4 : 8));
+    const size_t smem = (size_t)nt * a.K * sizeof(float);
+    if (smem > e->max_dyn_smem) return fail(e, SLLM_ERR_INVALID, "projection input does not fit shared memory");
+    const dim3 grid(gx, (n + nt - 1) / nt);
+    int rc;
+    switch (nt) {
+        case 1: rc = set_smem(e, k_gemv<WT, 1, MODE>, smem); if (rc) return rc;
+                return launch(e, k_gemv<WT, 1, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
+        case 2: rc = set_smem(e, k_gemv<WT, 2, MODE>, smem); if (rc) return rc;
+                return launch(e, k_gemv<WT, 2, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
+        case 4: rc = set_smem(e, k_gemv<WT, 4, MODE>, smem); if (rc) return rc;
+                return launch(e, k_gemv<WT, 4, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
+        default: rc = set_smem(e, k_gemv<WT, 8, MODE>, smem); if (rc) return rc;
+                return launch(e, k_gemv<WT, 8, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
+    }
+}
+
+template <typename KVT>
+int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
+    const dim3 grid(a.n_splits, a.m.H, a.pass.n_tok), block(kAttnThreads);
+    switch (a.m.hd) {
+        case 16: return launch(e, k_attn_decode<KVT, 16>, grid, block, 0, pdl, a);
+        case 32: return launch(e, k_attn_decode<KVT, 32>, grid, block, 0, pdl, a);
+        case 64: return launch(e, k_attn_decode<KVT, 64>, grid, block, 0, pdl, a);
+        case 128: return launch(e, k_attn_decode<KVT, 128>, grid, block, 0, pdl, a);
+    }
+    return fail(e, SLLM_ERR_INVALID, "unsupported head_dim");
+}
+
+// Runs the model over the pass's token list.  Logits are produced for n_rows rows
+// (row_tok[i] = pass-token index, NULL = identity) into `logits`.
+template <typename WT>
+int run_pass_t(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    const ModelDims& m = e->md;
+    KvView kv{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    const int n = pv.n_tok;
+    // attention split policy: fill the GPU when few (token, head) pairs exist
+    int n_splits = 1, kps = ((m.ctx + kPage - 1) / kPage) * kPage;
+    if (n <= e->split_tok_cap && n * m.H < 2 * e->sm_count) {
+        n_splits = std::min({kMaxSplits, e->pages_per_seq, std::max(1, 4 * e->sm_count / (n * m.H))});
+        const int pages_per_split = (e->pages_per_seq + n_splits - 1) / n_splits;
+        kps = pages_per_split * kPage;
+        n_splits = (e->pages_per_seq + pages_per_split - 1) / pages_per_split;
+    }
+    for (int l = 0; l < m.L; ++l) {
+        const LayerW& w = e->layers[l];
+        GemvArgs a{};
+        a.m = m; a.kv = kv; a.pass = pv; a.layer = l; a.rope = e->rope; a.eps = m.eps; a.n_tok = n;
+        // QKV (+ embedding gather on layer 0)
+        a.W = w.wqkv; a.R = 3 * m.D; a.K = m.D; a.in = e->x; a.gain = w.g_attn; a.out = e->q;
+        a.emb = (l == 0) ? e->emb_f32 : nullptr; a.x_out = e->x;
+        int rc = launch_gemv<WT, kModeQKV>(e, a, pdl);
+        if (rc) return rc;
+        AttnDecArgs t{};
+        t.q = e->q; t.out = e->att; t.m = m; t.kv = kv; t.pass = pv; t.layer = l;
+        t.n_splits = n_splits; t.keys_per_split = kps;
+        t.part_o = e->part_o; t.part_ml = e->part_ml; t.ticket = e->ticket;
+        rc = launch_attn<WT>(e, t, pdl);
+        if (rc) return rc;
+        a.emb = nullptr;
+        a.W = w.wo; a.R = m.D; a.K = m.D; a.in = e->att; a.out = e->x;
+        rc = launch_gemv<WT, kModeResidual>(e, a, pdl);
+        if (rc) return rc;
+        a.W = w.wgu; a.R = 2 * m.F; a.K = m.D; a.in = e->x; a.gain = w.g_ffn; a.out = e->hid;
+        rc = launch_gemv<WT, kModeGateUp>(e, a, pdl);
+        if (rc) return rc;
+        a.W = w.wd; a.R = m.D; a.K = m.F; a.in = e->hid; a.out = e->x;
+        rc = launch_gemv<WT, kModeResidual>(e, a, pdl);
+        if (rc) return rc;
+    }
+    if (n_rows > 0) {
+        GemvArgs a{};
+        a.m = m; a.eps = m.eps; a.W = e->emb_w; a.R = m.V; a.K = m.D; a.in = e->x; a.gain = e->g_final;
+        a.out = logits; a.n_tok = n_rows; a.row_tok = row_tok; a.pass = pv;
+        int rc = launch_gemv<WT, kModeHead>(e, a, pdl);
+        if (rc) return rc;
+    }
+    return SLLM_OK;
+}
+
+int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    return e->f32 ? run_pass_t<float>(e, pv, row_tok, n_rows, logits, pdl)
+                  : run_pass_t<__nv_bfloat16>(e, pv, row_tok, n_rows, logits, pdl);
+}
+
+template <typename WT, int MODE>
+int configure_gemv(sllm_engine* e) {
+    int rc = opt_in_smem(e, k_gemv<WT, 1, MODE>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 2, MODE>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 4, MODE>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 8, MODE>);
+    return rc;
+}
+template <typename WT>
+int configure_kernels_t(sllm_engine* e) {
+    int rc = configure_gemv<WT, kModeQKV>(e);
+    if (!rc) rc = configure_gemv<WT, kModeResidual>(e);
+    if (!rc) rc = configure_gemv<WT, kModeGateUp>(e);
+    if (!rc) rc = configure_gemv<WT, kModeHead>(e);
+    return rc;
+}
+int configure_kernels(sllm_engine* e);
+
+// ---- KV pages ------------------------------------------------------------------------------------------
+int ensure_pages(sllm_engine* e, int slot, int n_positions, bool* changed) {
+    const int need = (std::min(n_positions, e->md.ctx) + kPage - 1) / kPage;
+    auto& pages = e->slot_pages[slot];
+    while ((int)pages.size() < need) {
+        if (e->free_pages.empty()) return fail(e, SLLM_ERR_CAPACITY, "KV page pool exhausted");
+        pages.push_back(e->free_pages.back());
+        e->free_pages.pop_back();
+        *changed = true;
+    }
+    return SLLM_OK;
+}
+
+int upload_block_table(sllm_engine* e, int slot) {
+    const auto& pages = e->slot_pages[slot];
+    if (pages.empty()) return SLLM_OK;
+    CU(cudaMemcpyAsync(e->d_block_table + (size_t)slot * e->pages_per_seq, pages.data(), pages.size() * sizeof(int),
+                       cudaMemcpyHostToDevice, e->stream));
+    return SLLM_OK;
+}
+
+void release_slot(sllm_engine* e, int slot) {
+    for (int p : e->slot_pages[slot]) e->free_pages.push_back(p);
+    e->slot_pages[slot].clear();
+    e->h_len_bound[slot] = 0;
+}
+
+int sampling_check(sllm_engine* e, const sllm_sampling* o) {
+    if (!o) return fail(e, SLLM_ERR_INVALID, "sampling options missing");
+    if (o->temperature > 0.0f && !(o->top_p == o->top_p)) return fail(e, SLLM_ERR_INVALID, "top_p is NaN");
+    if (o->repetition_penalty == 0.0f) return fail(e, SLLM_ERR_INVALID, "repetition_penalty must be non-zero");
+    return SLLM_OK;
+}
+
+SampleArgs make_sample_args(sllm_engine* e, const sllm_sampling* o, int n_slots, const double* d_draws, int stride,
+                            int seeded) {
+    SampleArgs s{};
+    s.logits = e->step_logits; s.st = e->st; s.V = e->md.V; s.ctx = e->md.ctx;
+    s.temperature = o->temperature; s.top_p = o->top_p; s.penalty = o->repetition_penalty;
+    s.eos = o->eos_token; s.stop_token = o->stop_token;
+    s.draws = d_draws; s.n_slots = n_slots; s.draws_stride = stride; s.seeded = seeded;
+    s.next_tok_id = e->d_dec_id; s.next_tok_pos = e->d_dec_pos; s.next_tok_slot = e->d_dec_slot;
+    return s;
+}
+
+int configure_kernels(sllm_engine* e) {
+    // static shared memory of the sampler (histograms) counts against the same limit
+    cudaFuncAttributes fa{};
+    CU(cudaFuncGetAttributes(&fa, k_sample));
+    CU(cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                            (int)(e->max_dyn_smem - fa.sharedSizeBytes)));
+    if ((size_t)e->md.V * sizeof(float) + fa.sharedSizeBytes > e->max_dyn_smem)
+        return fail(e, SLLM_ERR_INVALID, "vocab_size does not fit the sampler's shared memory");
+    return e->f32 ? configure_kernels_t<float>(e) : configure_kernels_t<__nv_bfloat16>(e);
+}
+
+int launch_sampler(sllm_engine* e, const SampleArgs& s, bool pdl) {
+    const size_t smem = (size_t)e->md.V * sizeof(float);
+    int rc = set_smem(e, k_sample, smem);
+    if (rc) return rc;
+    return launch(e, k_sample, dim3(s.n_slots), dim3(kSampThreads), smem, pdl, s);
+}
+
+// host bound on lengths: one more token per live slot per sampling step
+int grow_for_step(sllm_engine* e) {
+    for (int s = 0; s < e->n_live; ++s) {
+        bool changed = false;
+        e->h_len_bound[s] = std::min(e->h_len_bound[s] + 1, e->md.ctx + 1);
+        int rc = ensure_pages(e, s, e->h_len_bound[s], &changed);
+        if (rc) return rc;
+        if (changed) { rc = upload_block_table(e, s); if (rc) return rc; }
+    }
+    return SLLM_OK;
+}
+
+PassView decode_view(sllm_engine* e) { return PassView{e->d_dec_id, e->d_dec_slot, e->d_dec_pos, e->n_live}; }
+
+// One decode iteration = sampler, then the model over the sampled tokens.
+int enqueue_iteration(sllm_engine* e, const SampleArgs& s) {
+    int rc = launch_sampler(e, s, true);
+    if (rc) return rc;
+    return run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, true);
+}
+
+int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* out) {
+    GraphKey k{};
+    k.n_slots = s.n_slots; k.t = s.temperature; k.p = s.top_p; k.pen = s.penalty; k.eos = s.eos; k.stop = s.stop_token;
+    k.seeded = s.seeded; k.stride = s.draws_stride; k.draws = s.draws;
+    auto it = e->graphs.find(k);
+    if (it != e->graphs.end()) { *out = it->second; return SLLM_OK; }
+    // run once outside capture so that every lazy attribute / module load has happened ...
+    // (not needed for correctness of results: capture replays the same launches)
+    cudaGraph_t g = nullptr;
+    const uint64_t before = e->launches;
+    CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_iteration(e, s);
+    cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    e->launches = before;
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (ce != cudaSuccess) return fail(e, SLLM_ERR_CUDA, std::string("graph capture failed: ") + cudaGetErrorString(ce));
+    cudaGraphExec_t ge = nullptr;
+    ce = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess) return fail(e, SLLM_ERR_CUDA, std::string("graph instantiate failed: ") + cudaGetErrorString(ce));
+    if (e->graphs.size() > 32) {
+        for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);
+        e->graphs.clear();
+    }
+    e->graphs[k] = ge;
+    *out = ge;
+    return SLLM_OK;
+}
+
+int launches_per_iteration(const sllm_engine* e) { return 1 + 5 * e->md.L + 1; }
+
+int check_finished_flags(sllm_engine* e, bool* all_done, bool* nonfinite) {
+    CU(cudaMemcpyAsync(e->h_flags, e->st.finished, e->n_live * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    *all_done = true; *nonfinite = false;
+    for (int s = 0; s < e->n_live; ++s) {
+        if (e->h_flags[s] == 0) *all_done = false;
+        if (e->h_flags[s] == 3) *nonfinite = true;
+    }
+    return SLLM_OK;
+}
+
+int upload_draws(sllm_engine* e, const double* host, size_t n_slots, size_t stride, bool transpose_from_step_major) {
+    const size_t n = n_slots * stride;
+    if (n > e->draws_cap) {
+        if (e->d_draws) {
+            CU(cudaStreamSynchronize(e->stream));
+            cudaFree(e->d_draws);
+            for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);   // they hold the old pointer
+            e->graphs.clear();
+        }
+        e->d_draws = nullptr;
+        CU(cudaMalloc((void**)&e->d_draws, n * sizeof(double)));
+        e->draws_cap = n;
+    }
+    if (!transpose_from_step_major || n_slots == 1) {
+        CU(cudaMemcpyAsync(e->d_draws, host, n * sizeof(double), cudaMemcpyHostToDevice, e->stream));
+        CU(cudaStreamSynchronize(e->stream));
+    } else {
+        std::vector<double> t(n);
+        for (size_t st = 0; st < stride; ++st)
+            for (size_t s = 0; s < n_slots; ++s) t[s * stride + st] = host[st * n_slots + s];
+        CU(cudaMemcpyAsync(e->d_draws, t.data(), n * sizeof(double), cudaMemcpyHostToDevice, e->stream));
+        CU(cudaStreamSynchronize(e->stream));
+    }
+    return SLLM_OK;
+}
+
+// generate_canonical<double,53>(std::mt19937_64): what std::discrete_distribution draws
+void canonical_stream(uint64_t seed, size_t n, double* out) {
+    std::mt19937_64 g(seed);
+    for (size_t i = 0; i < n; ++i) out[i] = std::generate_canonical<double, 53>(g);
+}
+
+int find_param(const sllm_engine* e, const char* name) {
+    for (size_t i = 0; i < e->params.size(); ++i) if (e->params[i].name == name) return (int)i;
+    return -1;
+}
+
+template <typename WT>
+int convert_param(sllm_engine* e, const ParamSlot& p) {
+    const ModelDims& m = e->md;
+    const size_t n = p.ndim == 2 ? p.dims[0] * p.dims[1] : p.dims[0];
+    auto transpose = [&](void* dst, int K, int N, int mul, int add, int row_off) -> int {
+        WT* d = static_cast<WT*>(dst) + (size_t)row_off * K;
+        const dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+        return launch(e, k_repack_transpose<WT>, grid, block, 0, false, (const float*)e->staging, d, K, N, mul, add);
+    };
+    LayerW* lw = p.layer >= 0 ? &e->layers[p.layer] : nullptr;
+    switch (p.kind) {
+        case 0: {
+            CU(cudaMemcpyAsync(e->emb_f32, e->staging, n * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
+            return launch(e, k_cast<WT>, dim3(e->sm_count * 8), dim3(256), 0, false, (const float*)e->staging,
+                          static_cast<WT*>(e->emb_w), n);
+        }
+        case 1: CU(cudaMemcpyAsync((void*)lw->g_attn, e->staging, n * 4, cudaMemcpyDeviceToDevice, e->stream)); return SLLM_OK;
+        case 6: CU(cudaMemcpyAsync((void*)lw->g_ffn, e->staging, n * 4, cudaMemcpyDeviceToDevice, e->stream)); return SLLM_OK;
+        case 10: CU(cudaMemcpyAsync(e->g_final, e->staging, n * 4, cudaMemcpyDeviceToDevice, e->stream)); return SLLM_OK;
+        case 2: return transpose((void*)lw->wqkv, m.D, m.D, 1, 0, 0);
+        case 3: return transpose((void*)lw->wqkv, m.D, m.D, 1, 0, m.D);
+        case 4: return transpose((void*)lw->wqkv, m.D, m.D, 1, 0, 2 * m.D);
+        case 5: return transpose((void*)lw->wo, m.D, m.D, 1, 0, 0);
+        case 7: return transpose((void*)lw->wgu, m.D, m.F, 2, 0, 0);
+        case 8: return transpose((void*)lw->wgu, m.D, m.F, 2, 1, 0);
+        case 9: return transpose((void*)lw->wd, m.F, m.D, 1, 0, 0);
+    }
+    return fail(e, SLLM_ERR_INVALID, "unknown parameter kind");
+}
+
+int set_param_impl(sllm_engine* e, int idx, const float* host) {
+    const ParamSlot& p = e->params[idx];
+    const size_t n = p.ndim == 2 ? p.dims[0] * p.dims[1] : p.dims[0];
+    CU(cudaMemcpyAsync(e->staging, host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    int rc = e->f32 ? convert_param<float>(e, p) : convert_param<__nv_bfloat16>(e, p);
+    if (rc) return rc;
+    CU(cudaStreamSynchronize(e->stream));      // the host buffer may be reused by the caller
+    return SLLM_OK;
+}
+
+int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq) {
+    const ModelDims& m = e->md;
+    if (n_seq == 0 || n_seq > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_CAPACITY, "n_seq exceeds max_batch");
+    size_t total = 0;
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        if (lens[s] == 0) return fail(e, SLLM_ERR_INVALID, "Inference::generate: prompt encoded to zero tokens");
+        if (lens[s] > (uint32_t)m.ctx) return fail(e, SLLM_ERR_INVALID, "Model::forward: seq_len exceeds context_length");
+        total += lens[s];
+    }
+    for (size_t i = 0; i < total; ++i)
+        if (ids[i] >= (uint32_t)m.V) return fail(e, SLLM_ERR_INVALID, "token id outside the vocabulary");
+    for (int s = 0; s < e->max_batch; ++s) release_slot(e, s);
+    e->n_live = (int)n_seq;
+    // slot state on the device
+    const int cap = e->st.tok_cap, words = m.V / 32;
+    std::vector<uint32_t> toks((size_t)n_seq * cap, 0), seen((size_t)n_seq * words, 0);
+    std::vector<int> ntok(n_seq), zeros(n_seq, 0);
+    size_t off = 0;
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        for (uint32_t i = 0; i < lens[s]; ++i) {
+            const uint32_t id = ids[off + i];
+            toks[(size_t)s * cap + i] = id;
+            seen[(size_t)s * words + (id >> 5)] |= 1u << (id & 31);
+        }
+        ntok[s] = (int)lens[s];
+        off += lens[s];
+        bool changed = false;
+        e->h_len_bound[s] = (int)lens[s];
+        int rc = ensure_pages(e, (int)s, (int)lens[s], &changed);
+        if (rc) return rc;
+        rc = upload_block_table(e, (int)s);
+        if (rc) return rc;
+    }
+    CU(cudaMemcpyAsync(e->st.tokens, toks.data(), toks.size() * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.seen, seen.data(), seen.size() * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.n_tok, ntok.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished, zeros.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.draw_idx, zeros.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return SLLM_OK;
+}
+
+// Runs every prompt position through the model in chunks.  want_all: logits of every position go
+// to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
+int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits) {
+    const ModelDims& m = e->md;
+    std::vector<uint32_t> c_id; std::vector<int> c_slot, c_pos, c_row; std::vector<int> c_row_dst;
+    c_id.reserve(e->pass_cap); c_slot.reserve(e->pass_cap); c_pos.reserve(e->pass_cap);
+    size_t off = 0, row_base = 0;
+    auto flush = [&]() -> int {
+        if (c_id.empty()) return SLLM_OK;
+        const int n = (int)c_id.size();
+        CU(cudaMemcpyAsync(e->d_tok_id, c_id.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
+        CU(cudaMemcpyAsync(e->d_tok_slot, c_slot.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
+        CU(cudaMemcpyAsync(e->d_tok_pos, c_pos.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
+        PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n};
+        int rc = run_pass(e, pv, nullptr, 0, nullptr, false);
+        if (rc) return rc;
+        // logits rows of this chunk, in groups that fit the logits buffer
+        for (size_t r0 = 0; r0 < c_row.size(); r0 += e->logit_rows_cap) {
+            const int nr = (int)std::min<size_t>(e->logit_rows_cap, c_row.size() - r0);
+            CU(cudaMemcpyAsync(e->d_row_tok, c_row.data() + r0, nr * 4, cudaMemcpyHostToDevice, e->stream));
+            GemvArgs a{};
+            a.m = m; a.eps = m.eps; a.W = e->emb_w; a.R = m.V; a.K = m.D; a.in = e->x; a.gain = e->g_final;
+            a.out = e->pass_logits; a.n_tok = nr; a.row_tok = e->d_row_tok; a.pass = pv;
+            rc = e->f32 ? launch_gemv<float, kModeHead>(e, a, false) : launch_gemv<__nv_bfloat16, kModeHead>(e, a, false);
+            if (rc) return rc;
+            if (host_logits) {
+                CU(cudaMemcpyAsync(host_logits + (row_base + r0) * m.V, e->pass_logits, (size_t)nr * m.V * 4,
+                                   cudaMemcpyDeviceToHost, e->stream));
+            } else {
+                for (int i = 0; i < nr; ++i)
+                    CU(cudaMemcpyAsync(e->step_logits + (size_t)c_row_dst[r0 + i] * m.V, e->pass_logits + (size_t)i * m.V,
+                                       (size_t)m.V * 4, cudaMemcpyDeviceToDevice, e->stream));
+            }
+            CU(cudaStreamSynchronize(e->stream));
+        }
+        row_base += c_row.size();
+        c_id.clear(); c_slot.clear(); c_pos.clear(); c_row.clear(); c_row_dst.clear();
+        return SLLM_OK;
+    };
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        for (uint32_t i = 0; i < lens[s]; ++i) {
+            if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
+            if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back((int)s); }
+            c_id.push_back(ids[off + i]); c_slot.push_back((int)s); c_pos.push_back((int)i);
+        }
+        off += lens[s];
+    }
+    return flush();
+}
+
+}  // namespace
+
+// =================================================================================== C ABI ===
+extern "C" {
+
+void sllm_default_model_config(sllm_model_config* c) {
+    c->vocab_size = 32768; c->context_length = 2048; c->num_layers = 16; c->d_model = 640;
+    c->num_heads = 10; c->ffn_hidden = 1728; c->rope_theta = 10000.0f; c->rms_eps = 1e-5f;
+}
+void sllm_default_engine_options(sllm_engine_options* o) {
+    std::memset(o, 0, sizeof *o);
+    o->max_batch = 1; o->weight_dtype = SLLM_WEIGHTS_BF16; o->kv_pages = 0; o->max_chunk_tokens = 0;
+    o->device = -1; o->use_graph = 1;
+}
+void sllm_default_sampling(sllm_sampling* s) {
+    s->temperature = 0.7f; s->top_p = 0.8f; s->repetition_penalty = 1.1f; s->eos_token = 32762;
+    s->stop_token = -1; s->seed = 1234;
+}
+
+const char* sllm_last_error(const sllm_engine* e) { return e ? e->err.c_str() : g_create_error.c_str(); }
+
+int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* opt_in, sllm_engine** out) {
+    if (!cfg || !out) return fail(nullptr, SLLM_ERR_INVALID, "sllm_engine_create: null argument");
+    *out = nullptr;
+    sllm_engine_options opt;
+    if (opt_in) opt = *opt_in; else sllm_default_engine_options(&opt);
+    const uint64_t V = cfg->vocab_size, D = cfg->d_model, H = cfg->num_heads, F = cfg->ffn_hidden, L = cfg->num_layers;
+    if (!V || !D || !H || !F || !L) return fail(nullptr, SLLM_ERR_INVALID, "model config has a zero dimension");
+    if (cfg->context_length == 0)
+        return fail(nullptr, SLLM_ERR_INVALID, "Inference::generate: context length must be greater than zero");
+    if (D % H) return fail(nullptr, SLLM_ERR_INVALID, "Attention: d_model must equal num_heads * head_dim");
+    const uint64_t hd = D / H;
+    if (hd != 16 && hd != 32 && hd != 64 && hd != 128) return fail(nullptr, SLLM_ERR_INVALID, "head_dim must be 16, 32, 64 or 128");
+    if (D % 8 || F % 8 || V % 64) return fail(nullptr, SLLM_ERR_INVALID, "d_model and ffn_hidden must be multiples of 8, vocab_size of 64");
+    if (V > 49152) return fail(nullptr, SLLM_ERR_INVALID, "vocab_size above 49152 does not fit the sampler's shared memory");
+    if (opt.max_batch == 0) return fail(nullptr, SLLM_ERR_INVALID, "max_batch must be at least 1");
+
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        return fail(nullptr, SLLM_ERR_CUDA, "no CUDA device: this library has no CPU path");
+    }
+    sllm_engine* e = new sllm_engine();
+    e->cfg = *cfg; e->opt = opt; e->f32 = opt.weight_dtype == SLLM_WEIGHTS_F32;
+    auto bail = [&](int rc) { g_create_error = e->err; sllm_engine_destroy(e); return rc; };
+    if (opt.device >= 0) { if (cudaSetDevice(opt.device) != cudaSuccess) { e->err = "cudaSetDevice failed"; return bail(SLLM_ERR_CUDA); } }
+    cudaGetDevice(&e->dev);
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, e->dev) != cudaSuccess) { e->err = "cudaGetDeviceProperties failed"; return bail(SLLM_ERR_CUDA); }
+    if (prop.major != 10) {
+        e->err = "device compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor) +
+                 " is not 10.x: the kernels are built for sm_100a only";
+        return bail(SLLM_ERR_CUDA);
+    }
+    e->sm_count = prop.multiProcessorCount;
+    e->max_dyn_smem = prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) { e->err = "cudaStreamCreate failed"; return bail(SLLM_ERR_CUDA); }
+    cudaEventCreate(&e->ev0); cudaEventCreate(&e->ev1);
+
+    ModelDims& m = e->md;
+    m.V = (int)V; m.ctx = (int)cfg->context_length; m.L = (int)L; m.D = (int)D; m.H = (int)H; m.hd = (int)hd; m.F = (int)F;
+    m.eps = cfg->rms_eps; m.scale = 1.0f / std::sqrt((float)hd);
+    e->max_batch = (int)opt.max_batch;
+    e->pages_per_seq = (m.ctx + kPage - 1) / kPage;
+    e->n_pages = opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq;
+    e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
+    e->pass_cap = std::max(e->pass_cap, e->max_batch);
+    e->logit_rows_cap = std::max(e->max_batch, 64);
+
+    // registry: src/model.cpp:106-131
+    auto add = [&](const std::string& n, uint64_t d0, uint64_t d1, int kind, int layer) {
+        ParamSlot p; p.name = n; p.dims[0] = d0; p.dims[1] = d1; p.ndim = d1 ? 2 : 1; p.kind = kind; p.layer = layer;
+        e->params.push_back(p);
+    };
+    add("embedding", V, D, 0, -1);
+    for (uint64_t l = 0; l < L; ++l) {
+        const std::string pre = "blocks." + std::to_string(l) + ".";
+        add(pre + "attn_norm", D, 0, 1, (int)l);
+        add(pre + "attn.q", D, D, 2, (int)l); add(pre + "attn.k", D, D, 3, (int)l);
+        add(pre + "attn.v", D, D, 4, (int)l); add(pre + "attn.out", D, D, 5, (int)l);
+        add(pre + "ffn_norm", D, 0, 6, (int)l);
+        add(pre + "ffn.gate", D, F, 7, (int)l); add(pre + "ffn.up", D, F, 8, (int)l); add(pre + "ffn.down", F, D, 9, (int)l);
+    }
+    add("final_norm", D, 0, 10, -1);
+
+    int rc = SLLM_OK;
+    const size_t ws = wsize(e);
+    auto A = [&](auto** p, size_t n, uint64_t* ctr) { if (!rc) rc = dalloc(e, p, n, ctr); };
+    // weights
+    unsigned char* tmp = nullptr;
+    A(&tmp, V * D * ws, &e->weight_bytes); e->emb_w = tmp;
+    A(&e->emb_f32, V * D, &e->weight_bytes);
+    A(&e->g_final, D, &e->weight_bytes);
+    e->layers.resize(L);
+    std::vector<float> ones(D, 1.0f);
+    for (uint64_t l = 0; l < L && !rc; ++l) {
+        LayerW& w = e->layers[l];
+        unsigned char* p = nullptr; float* g = nullptr;
+        A(&p, 3 * D * D * ws, &e->weight_bytes); w.wqkv = p;
+        A(&p, D * D * ws, &e->weight_bytes); w.wo = p;
+        A(&p, 2 * F * D * ws, &e->weight_bytes); w.wgu = p;
+        A(&p, D * F * ws, &e->weight_bytes); w.wd = p;
+        A(&g, D, &e->weight_bytes); w.g_attn = g;
+        A(&g, D, &e->weight_bytes); w.g_ffn = g;
+        if (!rc) {
+            cudaMemcpyAsync((void*)w.g_attn, ones.data(), D * 4, cudaMemcpyHostToDevice, e->stream);
+            cudaMemcpyAsync((void*)w.g_ffn, ones.data(), D * 4, cudaMemcpyHostToDevice, e->stream);
+        }
+    }
+    if (!rc) cudaMemcpyAsync(e->g_final, ones.data(), D * 4, cudaMemcpyHostToDevice, e->stream);
+    e->staging_elems = std::max<size_t>({V * D, D * F, D * D});
+    A(&e->staging, e->staging_elems, &e->scratch_bytes);
+    // RoPE table with the reference's fp32 expressions, src/ops/rope.cpp:48-56
+    {
+        std::vector<float2> tab((size_t)m.ctx * (hd / 2));
+        for (int pos = 0; pos < m.ctx; ++pos)
+            for (uint64_t i = 0; i < hd / 2; ++i) {
+                const float frequency = 1.0f / std::pow(cfg->rope_theta, static_cast<float>(2 * i) / static_cast<float>(hd));
+                const float angle = static_cast<float>(pos) * frequency;
+                tab[(size_t)pos * (hd / 2) + i] = make_float2(std::cos(angle), std::sin(angle));
+            }
+        A(&e->rope, tab.size(), &e->weight_bytes);
+        if (!rc) cudaMemcpyAsync(e->rope, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, e->stream);
+        if (!rc) cudaStreamSynchronize(e->stream);
+    }
+    // KV pool
+    {
+        unsigned char* p = nullptr;
+        const size_t page_bytes = 2 * H * kPage * hd * ws;
+        if (!rc) {
+            void* q = nullptr;
+            const size_t bytes = (size_t)L * e->n_pages * page_bytes;
+            cudaError_t ce = cudaMalloc(&q, bytes);
+            if (ce != cudaSuccess) { e->err = std::string("KV pool allocation failed: ") + cudaGetErrorString(ce); rc = SLLM_ERR_CUDA; }
+            else { e->allocs.push_back(q); e->kv_pool = q; e->kv_bytes = bytes; }
+        }
+        (void)p;
+        e->free_pages.resize(e->n_pages);
+        for (long long i = 0; i < e->n_pages; ++i) e->free_pages[i] = (int)(e->n_pages - 1 - i);
+        e->slot_pages.assign(e->max_batch, {});
+        e->h_len_bound.assign(e->max_batch, 0);
+        A(&e->d_block_table, (size_t)e->max_batch * e->pages_per_seq, &e->scratch_bytes);
+    }
+    // slot state
+    e->st.tok_cap = m.ctx + 1;
+    A(&e->st.tokens, (size_t)e->max_batch * e->st.tok_cap, &e->scratch_bytes);
+    A(&e->st.n_tok, e->max_batch, &e->scratch_bytes);
+    A(&e->st.finished, e->max_batch, &e->scratch_bytes);
+    A(&e->st.seen, (size_t)e->max_batch * (V / 32), &e->scratch_bytes);
+    A(&e->st.draw_idx, e->max_batch, &e->scratch_bytes);
+    // pass buffers
+    A(&e->d_tok_id, e->pass_cap, &e->scratch_bytes); A(&e->d_tok_slot, e->pass_cap, &e->scratch_bytes);
+    A(&e->d_tok_pos, e->pass_cap, &e->scratch_bytes);
+    A(&e->d_dec_id, e->max_batch, &e->scratch_bytes); A(&e->d_dec_slot, e->max_batch, &e->scratch_bytes);
+    A(&e->d_dec_pos, e->max_batch, &e->scratch_bytes);
+    A(&e->d_row_tok, e->pass_cap, &e->scratch_bytes);
+    A(&e->x, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->q, (size_t)e->pass_cap * D, &e->scratch_bytes);
+    A(&e->att, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->hid, (size_t)e->pass_cap * F, &e->scratch_bytes);
+    A(&e->step_logits, (size_t)e->max_batch * V, &e->scratch_bytes);
+    A(&e->pass_logits, (size_t)e->logit_rows_cap * V, &e->scratch_bytes);
+    A(&e->part_o, (size_t)e->split_tok_cap * H * kMaxSplits * hd, &e->scratch_bytes);
+    A(&e->part_ml, (size_t)e->split_tok_cap * H * kMaxSplits * 2, &e->scratch_bytes);
+    A(&e->ticket, (size_t)e->split_tok_cap * H, &e->scratch_bytes);
+    if (!rc && cudaMallocHost((void**)&e->h_flags, std::max(e->max_batch, 16) * sizeof(int)) != cudaSuccess) {
+        e->err = "cudaMallocHost failed"; rc = SLLM_ERR_CUDA;
+    }
+    if (!rc && cudaStreamSynchronize(e->stream) != cudaSuccess) { e->err = "initialisation failed"; rc = SLLM_ERR_CUDA; }
+    if (!rc) rc = configure_kernels(e);
+    if (rc) return bail(rc);
+    *out = e;
+    return SLLM_OK;
+}
+
+void sllm_engine_destroy(sllm_engine* e) {
+    if (!e) return;
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);
+    for (void* p : e->allocs) cudaFree(p);
+    if (e->d_draws) cudaFree(e->d_draws);
+    if (e->h_flags) cudaFreeHost(e->h_flags);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+int sllm_engine_stats(sllm_engine* e, sllm_stats* s) {
+    if (!e || !s) return SLLM_ERR_INVALID;
+    s->weight_bytes = e->weight_bytes; s->kv_bytes = e->kv_bytes; s->scratch_bytes = e->scratch_bytes;
+    s->kv_pages_total = (uint64_t)e->n_pages; s->kv_pages_free = e->free_pages.size();
+    s->launches = e->launches; s->decode_steps = e->decode_steps; s->last_step_ms = e->last_step_ms;
+    return SLLM_OK;
+}
+
+void* sllm_engine_stream(sllm_engine* e) { return e ? (void*)e->stream : nullptr; }
+
+uint32_t sllm_num_params(const sllm_engine* e) { return e ? (uint32_t)e->params.size() : 0; }
+
+int sllm_param_info(const sllm_engine* e, uint32_t i, char name[64], uint64_t dims[2], uint32_t* ndim) {
+    if (!e || i >= e->params.size()) return SLLM_ERR_INVALID;
+    const ParamSlot& p = e->params[i];
+    if (name) std::snprintf(name, 64, "%s", p.name.c_str());
+    if (dims) { dims[0] = p.dims[0]; dims[1] = p.dims[1]; }
+    if (ndim) *ndim = p.ndim;
+    return SLLM_OK;
+}
+
+int sllm_set_param(sllm_engine* e, const char* name, const float* host, const uint64_t* dims, uint32_t ndim) {
+    if (!e || !name || !host || !dims) return fail(e, SLLM_ERR_INVALID, "sllm_set_param: null argument");
+    const int idx = find_param(e, name);
+    if (idx < 0) return fail(e, SLLM_ERR_INVALID, std::string("unknown parameter '") + name + "'");
+    const ParamSlot& p = e->params[idx];
+    if (ndim != p.ndim || dims[0] != p.dims[0] || (ndim == 2 && dims[1] != p.dims[1]))
+        return fail(e, SLLM_ERR_INVALID, "load_checkpoint: shape mismatch for '" + p.name + "'");
+    return set_param_impl(e, idx, host);
+}
+
+int sllm_load_checkpoint(sllm_engine* e, const char* path, uint64_t* step, uint64_t* data_position) {
+    if (!e || !path) return fail(e, SLLM_ERR_INVALID, "sllm_load_checkpoint: null argument");
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return fail(e, SLLM_ERR_IO, std::string("load_checkpoint: cannot open ") + path);
+    uint64_t st = 0, dp = 0; uint32_t np = 0;
+    std::vector<float> host(e->staging_elems);
+    auto done = [&](int rc, const std::string& msg) { std::fclose(f); return fail(e, rc, msg); };
+    bool ok = std::fread(&st, 8, 1, f) == 1 && std::fread(&dp, 8, 1, f) == 1 && std::fread(&np, 4, 1, f) == 1;
+    if (ok && np != e->params.size()) return done(SLLM_ERR_IO, "load_checkpoint: parameter count differs (different model config?)");
+    for (size_t i = 0; ok && i < e->params.size(); ++i) {
+        const ParamSlot& p = e->params[i];
+        uint32_t nl = 0, nd = 0;
+        std::string name;
+        if (std::fread(&nl, 4, 1, f) == 1 && nl < 4096) { name.resize(nl); if (nl && std::fread(&name[0], 1, nl, f) != nl) name.clear(); }
+        if (name != p.name) return done(SLLM_ERR_IO, "load_checkpoint: expected parameter '" + p.name + "', file has '" + name + "'");
+        uint64_t dims[4] = {0, 0, 0, 0};
+        ok = std::fread(&nd, 4, 1, f) == 1 && nd <= 4;
+        for (uint32_t d = 0; ok && d < nd; ++d) ok = std::fread(&dims[d], 8, 1, f) == 1;
+        if (!ok) break;
+        if (nd != p.ndim || dims[0] != p.dims[0] || (nd == 2 && dims[1] != p.dims[1]))
+            return done(SLLM_ERR_IO, "load_checkpoint: shape mismatch for '" + p.name + "'");
+        const size_t n = p.ndim == 2 ? p.dims[0] * p.dims[1] : p.dims[0];
+        ok = std::fread(host.data(), sizeof(float), n, f) == n;
+        if (!ok) break;
+        int rc = set_param_impl(e, (int)i, host.data());
+        if (rc) { std::fclose(f); return rc; }
+    }
+    if (!ok) return done(SLLM_ERR_IO, "load_checkpoint: file truncated or corrupt");
+    std::fclose(f);
+    if (step) *step = st;
+    if (data_position) *data_position = dp;
+    return SLLM_OK;
+}
+
+int sllm_reset(sllm_engine* e) {
+    if (!e) return SLLM_ERR_INVALID;
+    for (int s = 0; s < e->max_batch; ++s) release_slot(e, s);
+    e->n_live = 0;
+    return SLLM_OK;
+}
+
+int sllm_prefill(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq) {
+    if (!e || !ids || !lens) return fail(e, SLLM_ERR_INVALID, "sllm_prefill: null argument");
+    int rc = load_slots(e, ids, lens, n_seq);
+    if (rc) return rc;
+    return prefill_impl(e, ids, lens, n_seq, nullptr);
+}
+
+int sllm_forward_logits(sllm_engine* e, const uint32_t* ids, uint64_t B, uint64_t T, float* host_logits) {
+    if (!e || !ids || !host_logits) return fail(e, SLLM_ERR_INVALID, "sllm_forward_logits: null argument");
+    if (T > (uint64_t)e->md.ctx) return fail(e, SLLM_ERR_INVALID, "Model::forward: seq_len exceeds context_length");
+    if (B == 0 || T == 0) return SLLM_OK;
+    // rows beyond max_batch are processed in groups of max_batch sequences
+    for (uint64_t b0 = 0; b0 < B; b0 += e->max_batch) {
+        const uint32_t nb = (uint32_t)std::min<uint64_t>(e->max_batch, B - b0);
+        std::vector<uint32_t> lens(nb, (uint32_t)T);
+        int rc = load_slots(e, ids + b0 * T, lens.data(), nb);
+        if (rc) return rc;
+        rc = prefill_impl(e, ids + b0 * T, lens.data(), nb, host_logits + b0 * T * e->md.V);
+        if (rc) return rc;
+    }
+    return SLLM_OK;
+}
+
+int sllm_sample(sllm_engine* e, const sllm_sampling* opt, const double* draws) {
+    if (!e) return SLLM_ERR_INVALID;
+    int rc = sampling_check(e, opt);
+    if (rc) return rc;
+    if (e->n_live == 0) return fail(e, SLLM_ERR_STATE, "sllm_sample: no live slots");
+    if (opt->temperature > 0.0f && !draws) return fail(e, SLLM_ERR_INVALID, "sllm_sample: draws required when temperature > 0");
+    const double* dd = nullptr;
+    if (draws && opt->temperature > 0.0f) {
+        rc = upload_draws(e, draws, e->n_live, 1, false);
+        if (rc) return rc;
+        dd = e->d_draws;
+        CU(cudaMemsetAsync(e->st.draw_idx, 0, e->n_live * sizeof(int), e->stream));
+    }
+    rc = grow_for_step(e);
+    if (rc) return rc;
+    SampleArgs s = make_sample_args(e, opt, e->n_live, dd, 1, 0);
+    rc = launch_sampler(e, s, false);
+    if (rc) return rc;
+    bool all_done, nonfinite;
+    rc = check_finished_flags(e, &all_done, &nonfinite);
+    if (rc) return rc;
+    if (nonfinite) return fail(e, SLLM_ERR_NONFINITE, "Inference::generate: all logits are non-finite");
+    return SLLM_OK;
+}
+
+int sllm_decode_step(sllm_engine* e) {
+    if (!e) return SLLM_ERR_INVALID;
+    if (e->n_live == 0) return fail(e, SLLM_ERR_STATE, "sllm_decode_step: no live slots");
+    CU(cudaEventRecord(e->ev0, e->stream));
+    int rc = run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, false);
+    if (rc) return rc;
+    CU(cudaEventRecord(e->ev1, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    cudaEventElapsedTime(&e->last_step_ms, e->ev0, e->ev1);
+    e->decode_steps += 1;
+    return SLLM_OK;
+}
+
+int sllm_get_step_logits(sllm_engine* e, uint32_t slot, float* host) {
+    if (!e || !host || slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_get_step_logits: bad argument");
+    CU(cudaMemcpyAsync(host, e->step_logits + (size_t)slot * e->md.V, (size_t)e->md.V * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return SLLM_OK;
+}
+
+int sllm_set_step_logits(sllm_engine* e, uint32_t slot, const float* host) {
+    if (!e || !host || slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_set_step_logits: bad argument");
+    CU(cudaMemcpyAsync(e->step_logits + (size_t)slot * e->md.V, host, (size_t)e->md.V * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return SLLM_OK;
+}
+
+int sllm_get_tokens(sllm_engine* e, uint32_t slot, uint32_t* out, uint64_t capacity, uint64_t* n) {
+    if (!e || !n || slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_get_tokens: bad argument");
+    int nt = 0;
+    CU(cudaMemcpyAsync(&nt, e->st.n_tok + slot, 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    *n = (uint64_t)nt;
+    if (out) {
+        const size_t c = std::min<uint64_t>(capacity, (uint64_t)nt);
+        CU(cudaMemcpyAsync(out, e->st.tokens + (size_t)slot * e->st.tok_cap, c * 4, cudaMemcpyDeviceToHost, e->stream));
+        CU(cudaStreamSynchronize(e->stream));
+    }
+    return SLLM_OK;
+}
+
+int sllm_force_token(sllm_engine* e, uint32_t slot, uint32_t token) {
+    if (!e || slot >= (uint32_t)e->n_live) return fail(e, SLLM_ERR_INVALID, "sllm_force_token: bad slot");
+    if (token >= (uint32_t)e->md.V) return fail(e, SLLM_ERR_INVALID, "token id outside the vocabulary");
+    int nt = 0;
+    CU(cudaMemcpyAsync(&nt, e->st.n_tok + slot, 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    if (nt < 1) return fail(e, SLLM_ERR_STATE, "sllm_force_token: empty slot");
+    const int words = e->md.V / 32;
+    std::vector<uint32_t> toks(nt), seen(words, 0);
+    CU(cudaMemcpyAsync(toks.data(), e->st.tokens + (size_t)slot * e->st.tok_cap, (size_t)nt * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    toks[nt - 1] = token;
+    for (uint32_t id : toks) seen[id >> 5] |= 1u << (id & 31);
+    const int zero = 0;
+    CU(cudaMemcpyAsync(e->st.seen + (size_t)slot * words, seen.data(), words * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.tokens + (size_t)slot * e->st.tok_cap + (nt - 1), &token, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_id + slot, &token, 4, cudaMemcpyHostToDevice, e->stream));
+    if (nt <= e->md.ctx) CU(cudaMemcpyAsync(e->st.finished + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return SLLM_OK;
+}
+
+int sllm_truncate(sllm_engine* e, uint32_t slot, uint64_t n_tokens) {
+    if (!e || slot >= (uint32_t)e->n_live) return fail(e, SLLM_ERR_INVALID, "sllm_truncate: bad slot");
+    const int cap = e->st.tok_cap, V = e->md.V, words = V / 32;
+    int nt = 0;
+    CU(cudaMemcpyAsync(&nt, e->st.n_tok + slot, 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    if (n_tokens < 1 || n_tokens > (uint64_t)nt) return fail(e, SLLM_ERR_INVALID, "sllm_truncate: length out of range");
+    std::vector<uint32_t> toks(n_tokens), seen(words, 0);
+    CU(cudaMemcpyAsync(toks.data(), e->st.tokens + (size_t)slot * cap, n_tokens * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    for (uint32_t id : toks) seen[id >> 5] |= 1u << (id & 31);
+    const int n = (int)n_tokens, zero = 0, pos = n - 1;
+    const int slot_i = (int)slot;
+    CU(cudaMemcpyAsync(e->st.seen + (size_t)slot * words, seen.data(), words * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.n_tok + slot, &n, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.draw_idx + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_id + slot, &toks[n - 1], 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_pos + slot, &pos, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_slot + slot, &slot_i, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    e->h_len_bound[slot] = n;
+    return SLLM_OK;
+}
+
+// n_steps x (sampler, model pass) on the device; slots must have step logits (after prefill).
+static int decode_loop_impl(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* d_draws, int stride,
+                            int seeded, bool last_pass, bool* all_done_out) {
+    SampleArgs s = make_sample_args(e, opt, e->n_live, d_draws, stride, seeded);
+    cudaGraphExec_t ge = nullptr;
+    if (e->opt.use_graph) { int rc = get_iteration_graph(e, s, &ge); if (rc) return rc; }
+    const uint64_t check_every = 64;
+    for (uint64_t i = 0; i < n_steps; ++i) {
+        int rc = grow_for_step(e);
+        if (rc) return rc;
+        const bool final_one = (i + 1 == n_steps) && !last_pass;
+        if (final_one) {
+            rc = launch_sampler(e, s, false);
+            if (rc) return rc;
+        } else if (ge) {
+            CU(cudaGraphLaunch(ge, e->stream));
+            e->launches += launches_per_iteration(e);
+        } else {
+            rc = enqueue_iteration(e, s);
+            if (rc) return rc;
+        }
+        e->decode_steps += final_one ? 0 : 1;
+        if ((i + 1) % check_every == 0 || i + 1 == n_steps) {
+            bool all_done, nonfinite;
+            rc = check_finished_flags(e, &all_done, &nonfinite);
+            if (rc) return rc;
+            if (nonfinite) return fail(e, SLLM_ERR_NONFINITE, "Inference::generate: all logits are non-finite");
+            if (all_done_out) *all_done_out = all_done;
+            if (all_done) break;
+        }
+    }
+    return SLLM_OK;
+}
+
+int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws) {
+    if (!e) return SLLM_ERR_INVALID;
+    int rc = sampling_check(e, opt);
+    if (rc) return rc;
+    if (e->n_live == 0) return fail(e, SLLM_ERR_STATE, "sllm_decode_loop: no live slots");
+    if (n_steps == 0) return SLLM_OK;
+    const double* dd = nullptr;
+    if (opt->temperature > 0.0f) {
+        if (!draws) return fail(e, SLLM_ERR_INVALID, "sllm_decode_loop: draws required when temperature > 0");
+        rc = upload_draws(e, draws, e->n_live, n_steps, true);
+        if (rc) return rc;
+        dd = e->d_draws;
+        CU(cudaMemsetAsync(e->st.draw_idx, 0, e->n_live * sizeof(int), e->stream));
+    }
+    return decode_loop_impl(e, n_steps, opt, dd, (int)n_steps, 0, true, nullptr);
+}
+
+int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, uint64_t max_new,
+                  const sllm_sampling* opt, const double* draws, uint32_t* out, uint64_t out_stride, uint64_t* out_lens) {
+    if (!e || !ids || !lens || !out || !out_lens) return fail(e, SLLM_ERR_INVALID, "sllm_generate: null argument");
+    int rc = sampling_check(e, opt);
+    if (rc) return rc;
+    rc = load_slots(e, ids, lens, n_seq);
+    if (rc) return rc;
+    if (max_new > 0) {
+        const double* dd = nullptr;
+        int seeded = 0;
+        if (opt->temperature > 0.0f) {
+            if (draws) {
+                rc = upload_draws(e, draws, n_seq, max_new, true);
+            } else {
+                seeded = 1;
+                std::vector<double> t((size_t)n_seq * max_new);
+                for (uint32_t s = 0; s < n_seq; ++s) canonical_stream(opt->seed + s, max_new, t.data() + (size_t)s * max_new);
+                rc = upload_draws(e, t.data(), n_seq, max_new, false);
+            }
+            if (rc) return rc;
+            dd = e->d_draws;
+        }
+        rc = prefill_impl(e, ids, lens, n_seq, nullptr);
+        if (rc) return rc;
+        rc = decode_loop_impl(e, max_new, opt, dd, (int)max_new, seeded, false, nullptr);
+        if (rc) return rc;
+    }
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        rc = sllm_get_tokens(e, s, out + (size_t)s * out_stride, out_stride, &out_lens[s]);
+        if (rc) return rc;
+    }
+    return SLLM_OK;
+}
+
+}  // extern "C"

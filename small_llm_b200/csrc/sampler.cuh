@@ -1,0 +1,309 @@
+// On-device sampler: one block per live sequence slot.
+//
+// Follows the reference's host sampler (src/inference.cpp:101-160):
+//   repetition penalty once per distinct id of the slot's whole history (:104-112),
+//   greedy = first maximum (:116-119), else weights expf((s - max)/T) (:126-131),
+//   candidates in descending probability (:138), the shortest prefix whose probability mass
+//   reaches top_p (:141-148), a draw from the kept candidates by inverse CDF in that order
+//   (std::discrete_distribution, :151-154), append, stop on EOS / stop token (:158-160).
+// No sort is performed.  Probability mass is held as 64-bit fixed point (weight * 2^47, exact for
+// every weight >= 2^-24), so partial sums are associative and the result is independent of the
+// order in which threads add.  "The element at which the descending cumulative mass first reaches
+// a target" is found by bucket refinement over the weights' float bit patterns: <= 4 histogram
+// passes of 1024 buckets, then ties (equal weights) are resolved towards the lower id.
+#pragma once
+#include "common.cuh"
+
+namespace sllm {
+
+constexpr int kSampThreads = 1024;
+constexpr int kSampBuckets = 1024;
+constexpr int kFixShift = 47;
+
+struct SeqState {                 // device arrays indexed by slot
+    uint32_t* tokens;             // [max_batch][tok_cap]
+    int* n_tok;                   // tokens held (prompt + continuation)
+    int* finished;                // 0 live, 1 EOS/stop, 2 context exhausted, 3 non-finite logits
+    uint32_t* seen;               // [max_batch][V/32] bitmap of ids in the history
+    int* draw_idx;                // next entry of the slot's draw list
+    int tok_cap;
+};
+
+struct SampleArgs {
+    const float* logits;          // [n_slots][V] step logits
+    SeqState st;
+    int V, ctx;
+    float temperature, top_p, penalty;
+    uint32_t eos;
+    long long stop_token;
+    const double* draws;          // device [n_slots][draws_stride]; entry draw_idx[slot] is used
+    int n_slots;
+    int draws_stride;
+    int seeded;                   // 0: one entry per sampling step.  1: an entry is consumed only when at least
+                                  //    two candidates are kept (std::discrete_distribution's behaviour)
+    // next-pass token list, written for the decode step that follows
+    uint32_t* next_tok_id;
+    int* next_tok_pos;
+    int* next_tok_slot;
+};
+
+struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned int cnt_above, ties, r; int found; };
+
+__device__ __forceinline__ unsigned long long fix_of(float w) {
+    return (unsigned long long)((double)w * (double)(1ull << kFixShift));
+}
+
+// Finds the element, in descending (key, then ascending id) order, at which the running mass
+// first reaches `target`.  All threads of the block call it with the same arguments.
+__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t kmin, uint32_t kmax,
+                                    unsigned long long* h_mass, unsigned int* h_cnt, int* s_pick) {
+    const int tid = threadIdx.x;
+    uint32_t lo = kmin, hi = kmax;
+    unsigned long long cum = 0;      // mass of keys > hi
+    unsigned int cnt = 0;            // elements with key > hi
+    SelectResult res;
+    res.found = 0;
+    for (int pass = 0; pass < 5; ++pass) {
+        const uint32_t width = hi - lo;              // inclusive range has width+1 keys
+        int sh = 0;
+        while ((width >> sh) >= (uint32_t)kSampBuckets) ++sh;
+        for (int b = tid; b < kSampBuckets; b += kSampThreads) { h_mass[b] = 0; h_cnt[b] = 0; }
+        if (tid == 0) *s_pick = kSampBuckets;
+        __syncthreads();
+        for (int i = tid; i < V; i += kSampThreads) {
+            const uint32_t key = __float_as_uint(w[i]);
+            if (key >= lo && key <= hi) {
+                const int b = (int)((key - lo) >> sh);
+                atomicAdd(&h_mass[b], fix_of(w[i]));
+                atomicAdd(&h_cnt[b], 1u);
+            }
+        }
+        __syncthreads();
+        // thread j looks at bucket (top - j): descending order; block-wide inclusive scan
+        const int top = (int)(width >> sh);
+        __shared__ unsigned long long sc_m[32];
+        __shared__ unsigned int sc_c[32];
+        unsigned long long my_m = 0; unsigned int my_c = 0;
+        const int b = top - tid;
+        if (b >= 0) { my_m = h_mass[b]; my_c = h_cnt[b]; }
+        unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
+        const int lane = tid & 31, wp = tid >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long m2 = __shfl_up_sync(0xffffffffu, inc_m, o);
+            const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc_c, o);
+            if (lane >= o) { inc_m += m2; inc_c += c2; }
+        }
+        if (lane == 31) { sc_m[wp] = inc_m; sc_c[wp] = inc_c; }
+        __syncthreads();
+        unsigned long long off_m = 0; unsigned int off_c = 0;
+        for (int k = 0; k < wp; ++k) { off_m += sc_m[k]; off_c += sc_c[k]; }
+        inc_m += off_m; inc_c += off_c;
+        if (b >= 0 && my_c > 0 && cum + inc_m >= target) atomicMin(s_pick, tid);
+        __syncthreads();
+        const int pick = *s_pick;
+        if (pick == kSampBuckets) {           // target beyond all the mass in range
+            res.found = 0; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.qk = 0; res.ties = 0; res.r = 0;
+            // report totals of the whole range as "above"
+            __shared__ unsigned long long tot_m; __shared__ unsigned int tot_c;
+            if (tid == kSampThreads - 1) { tot_m = inc_m; tot_c = inc_c; }
+            __syncthreads();
+            res.cum_above = cum + tot_m; res.cnt_above = cnt + tot_c;
+            __syncthreads();
+            return res;
+        }
+        __shared__ unsigned long long pk_m, pk_em; __shared__ unsigned int pk_c, pk_ec;
+        if (tid == pick) { pk_m = inc_m - my_m; pk_c = inc_c - my_c; pk_em = my_m; pk_ec = my_c; }
+        __syncthreads();
+        cum += pk_m; cnt += pk_c;
+        const int pb = top - pick;
+        const uint32_t nlo = lo + ((uint32_t)pb << sh);
+        uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
+        if (nhi > hi) nhi = hi;
+        const unsigned long long em = pk_em; const unsigned int ec = pk_ec;
+        __syncthreads();
+        lo = nlo; hi = nhi;
+        if (sh == 0) {                       // one key per bucket: done
+            res.found = 1; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.ties = ec;
+            res.qk = em / ec;
+            unsigned long long need = target > cum ? target - cum : 0;
+            unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
+            if (r < 1) r = 1;
+            if (r > ec) r = ec;
+            res.r = (unsigned int)r;
+            return res;
+        }
+    }
+    res.found = 0; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.qk = 0; res.ties = 0; res.r = 0;
+    return res;
+}
+
+// id of the r-th (1-based) lowest index whose weight has bit pattern `key`
+__device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r, unsigned int* s_scan, int* s_out) {
+    const int tid = threadIdx.x;
+    const int per = (V + kSampThreads - 1) / kSampThreads;
+    const int b = tid * per, e = min(V, b + per);
+    unsigned int c = 0;
+    for (int i = b; i < e; ++i) c += (__float_as_uint(w[i]) == key);
+    // exclusive scan of c over threads
+    unsigned int inc = c;
+    const int lane = tid & 31, wp = tid >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += c2;
+    }
+    if (lane == 31) s_scan[wp] = inc;
+    if (tid == 0) *s_out = -1;
+    __syncthreads();
+    unsigned int off = 0;
+    for (int k = 0; k < wp; ++k) off += s_scan[k];
+    const unsigned int before = off + inc - c;
+    if (c > 0 && r > before && r <= before + c) {
+        unsigned int seen = before;
+        for (int i = b; i < e; ++i)
+            if (__float_as_uint(w[i]) == key && ++seen == r) { *s_out = i; break; }
+    }
+    __syncthreads();
+    const int out = *s_out;
+    __syncthreads();
+    return out;
+}
+
+__global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
+    extern __shared__ __align__(16) float w[];                 // [V] scores, then weights
+    __shared__ unsigned long long h_mass[kSampBuckets];
+    __shared__ unsigned int h_cnt[kSampBuckets];
+    __shared__ float r_val[32];
+    __shared__ int r_idx[32];
+    __shared__ unsigned long long r_sum[32];
+    __shared__ uint32_t r_kmin[32];
+    __shared__ unsigned int s_scan[32];
+    __shared__ int s_pick, s_out;
+    __shared__ float s_max; __shared__ int s_arg;
+    __shared__ unsigned long long s_total; __shared__ uint32_t s_kmin;
+
+    const int slot = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int V = a.V;
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    int n_tok = a.st.n_tok[slot];
+    const int fin = a.st.finished[slot];
+    int token = -1;
+
+    if (!fin) {
+        const float* lg = a.logits + (size_t)slot * V;
+        const uint32_t* seen = a.st.seen + (size_t)slot * (V / 32);
+        // ---- penalty + first maximum --------------------------------------------------------
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = tid; i < V; i += kSampThreads) {
+            float s = lg[i];
+            if (a.penalty != 1.0f && ((seen[i >> 5] >> (i & 31)) & 1u)) s = s > 0.f ? s / a.penalty : s * a.penalty;
+            w[i] = s;
+            if (s > bv) { bv = s; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (v2 > bv || (v2 == bv && i2 < bi)) { bv = v2; bi = i2; }
+        }
+        if (lane == 0) { r_val[wp] = bv; r_idx[wp] = bi; }
+        __syncthreads();
+        if (wp == 0) {
+            bv = r_val[lane]; bi = r_idx[lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (v2 > bv || (v2 == bv && i2 < bi)) { bv = v2; bi = i2; }
+            }
+            if (lane == 0) { s_max = bv; s_arg = bi; }
+        }
+        __syncthreads();
+        const float mx = s_max;
+        if (!isfinite(mx)) {
+            if (tid == 0) a.st.finished[slot] = 3;
+        } else if (a.temperature <= 0.0f) {
+            token = s_arg;
+        } else {
+            // ---- weights, total mass, smallest key ---------------------------------------------
+            unsigned long long sum = 0; uint32_t kmin = 0xffffffffu;
+            for (int i = tid; i < V; i += kSampThreads) {
+                const float e = expf((w[i] - mx) / a.temperature);
+                w[i] = e;
+                sum += fix_of(e);
+                kmin = min(kmin, __float_as_uint(e));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+            }
+            if (lane == 0) { r_sum[wp] = sum; r_kmin[wp] = kmin; }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long t = 0; uint32_t k = 0xffffffffu;
+                for (int i = 0; i < 32; ++i) { t += r_sum[i]; k = min(k, r_kmin[i]); }
+                s_total = t; s_kmin = k;
+            }
+            __syncthreads();
+            const unsigned long long total = s_total;
+            const uint32_t kmax = __float_as_uint(1.0f);      // the maximum's weight is exp(0) = 1
+            // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
+            unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
+            if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
+            SelectResult cut = select_mass(w, V, t1, s_kmin, kmax, h_mass, h_cnt, &s_pick);
+            unsigned long long kept_mass; unsigned int kept;
+            if (cut.found) { kept_mass = cut.cum_above + (unsigned long long)cut.r * cut.qk; kept = cut.cnt_above + cut.r; }
+            else { kept_mass = cut.cum_above; kept = cut.cnt_above; }
+            // ---- the draw -------------------------------------------------------------------------
+            double u = 0.0;
+            if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
+            unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
+            if (t2 > kept_mass) t2 = kept_mass;
+            SelectResult hit = select_mass(w, V, t2, s_kmin, kmax, h_mass, h_cnt, &s_pick);
+            uint32_t key; unsigned int r;
+            if (hit.found && (hit.cnt_above + hit.r) <= kept) { key = hit.key; r = hit.r; }
+            else if (cut.found) { key = cut.key; r = cut.r; }                  // last kept candidate
+            else { key = s_kmin; r = 0xffffffffu; }
+            if (r == 0xffffffffu) {                                            // last of everything: highest id of the smallest key
+                unsigned int c = 0;
+                for (int i = tid; i < V; i += kSampThreads) c += (__float_as_uint(w[i]) == key);
+                c = __reduce_add_sync(0xffffffffu, c);
+                if (lane == 0) s_scan[wp] = c;
+                __syncthreads();
+                unsigned int t = 0;
+                for (int i = 0; i < 32; ++i) t += s_scan[i];
+                __syncthreads();
+                r = t;
+            }
+            token = nth_with_key(w, V, key, r, s_scan, &s_out);
+            if (tid == 0 && (!a.seeded || kept >= 2)) a.st.draw_idx[slot] += 1;
+        }
+    }
+
+    // ---- append, stop rules, next pass inputs ------------------------------------------------------
+    if (tid == 0) {
+        int f = a.st.finished[slot];
+        if (!f && token >= 0) {
+            a.st.tokens[(size_t)slot * a.st.tok_cap + n_tok] = (uint32_t)token;
+            n_tok += 1;
+            a.st.n_tok[slot] = n_tok;
+            atomicOr(&a.st.seen[(size_t)slot * (V / 32) + (token >> 5)], 1u << (token & 31));
+            if ((uint32_t)token == a.eos || (long long)token == a.stop_token) f = 1;
+            else if (n_tok > a.ctx) f = 2;
+            a.st.finished[slot] = f;
+        }
+        // the decode step that follows feeds the last token at position n_tok-1; finished slots
+        // repeat their last position (idempotent) so the launch shape stays fixed
+        const int p = min(n_tok - 1, a.ctx - 1);
+        a.next_tok_id[slot] = a.st.tokens[(size_t)slot * a.st.tok_cap + p];
+        a.next_tok_pos[slot] = p;
+        a.next_tok_slot[slot] = slot;
+    }
+}
+
+}  // namespace sllm
