@@ -1,0 +1,3 @@
+// Forwarding header: small-llm code that includes "tokenizer.h" finds the same names in small_llm.hpp.
+#pragma once
+#include "small_llm.hpp"
