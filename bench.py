@@ -157,7 +157,8 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     eng.prefill([prompt])
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.profile_only else max(args.warmup, 3)
+    for _ in range(n_warm):
         one_generation()
     launches0 = eng.stats()["launches"]
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -203,7 +204,7 @@ def run_ours(args):
         achieved = bytes_tok / (step_ms * 1e-3) / 1e9
         line = {
             "metric": "decode tok/s at batch 1 (1 B200) vs HBM roofline; p50 per-token ms",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": ms / args.steps, "per_token_ms": step_ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 weights+KV, f32 accumulate",
             "data": "synthetic: N(0,0.02) weights (numpy seed 0), std::mt19937 prompt ids and draws",
@@ -219,6 +220,8 @@ def run_ours(args):
                          "peak_kind": peak_kind, "algorithmic_bytes_per_token": bytes_tok, "traffic": None},
             "clocks": clocks.summary(),
         }
+        if args.profile_only:
+            line["profile_only"] = True
         if args.cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
         print(json.dumps(line))
@@ -300,13 +303,22 @@ def run_reference(args):
 
 
 def main():
+    global N_NEW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--decode-steps", type=int, default=N_NEW,
+                    help="profiling only: shorter generations (the printed value is then not a benchmark figure)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
+    if args.decode_steps != N_NEW:
+        N_NEW = args.decode_steps
+        args.profile_only = True
+        args.cpu_baseline = False
+    else:
+        args.profile_only = False
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -16,6 +16,7 @@ namespace sllm {
 struct AttnDecArgs {
     const float* q;        // [n_tok][D] rotated queries (fp32)
     float* out;            // [n_tok][D] merged heads
+    __nv_bfloat16* out_bf16; // when set, the result is also stored as bf16 (operand of the tensor-core out-projection)
     ModelDims m;
     KvView kv;
     PassView pass;
@@ -132,7 +133,10 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const AttnDecArgs 
     }
 
     if (a.n_splits == 1) {
-        if (tid < HD) a.out[(size_t)tok * D + head * HD + tid] = o / l;
+        if (tid < HD) {
+            a.out[(size_t)tok * D + head * HD + tid] = o / l;
+            if (a.out_bf16) a.out_bf16[(size_t)tok * D + head * HD + tid] = __float2bfloat16_rn(o / l);
+        }
         return;
     }
 
@@ -162,6 +166,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const AttnDecArgs 
             num += w * __ldcg(a.part_o + (base + s) * HD + tid);
         }
         a.out[(size_t)tok * D + head * HD + tid] = num / den;
+        if (a.out_bf16) a.out_bf16[(size_t)tok * D + head * HD + tid] = __float2bfloat16_rn(num / den);
     }
     if (tid == 0) a.ticket[(size_t)tok * a.m.H + head] = 0;   // ready for the next launch
 }

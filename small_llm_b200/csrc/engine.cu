@@ -23,6 +23,7 @@
 #include "../../include/sllm.h"
 #include "attn_decode.cuh"
 #include "common.cuh"
+#include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "repack.cuh"
 #include "sampler.cuh"
@@ -96,6 +97,14 @@ struct sllm_engine {
     float* step_logits = nullptr;      // [max_batch][V]
     float* pass_logits = nullptr;      // [logit_rows_cap][V]
     int logit_rows_cap = 0;
+    // tensor-core path (bf16 weights, passes of >= tc_min_tokens tokens)
+    __nv_bfloat16* xn16 = nullptr; __nv_bfloat16* att16 = nullptr; __nv_bfloat16* hid16 = nullptr; __nv_bfloat16* head16 = nullptr;
+    unsigned int* d_status = nullptr;
+    void* encode_tiled = nullptr;                    // cuTensorMapEncodeTiled
+    std::vector<CUtensorMap> map_wqkv, map_wo, map_wgu, map_wd;
+    CUtensorMap map_head{};
+    std::map<std::pair<const void*, int>, CUtensorMap> map_x;    // (activation buffer, BN) -> map
+    int tc_min_tokens = 17;
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
@@ -166,7 +175,11 @@ int set_smem(sllm_engine*, K, size_t) { return SLLM_OK; }
 
 template <typename K>
 int opt_in_smem(sllm_engine* e, K kern) {
-    CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->max_dyn_smem));
+    // the opt-in limit covers static + dynamic shared memory of the kernel
+    cudaFuncAttributes fa{};
+    CU(cudaFuncGetAttributes(&fa, kern));
+    CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                            (int)(e->max_dyn_smem - fa.sharedSizeBytes)));
     return SLLM_OK;
 }
 
@@ -178,7 +191,7 @@ int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
     const int n = a.n_tok;
     int nt = n == 1 ? 1 : (n == 2 ? 2 : (n <= 4 ? 4 : 8));
     const size_t smem = (size_t)nt * a.K * sizeof(float);
-    if (smem > e->max_dyn_smem) return fail(e, SLLM_ERR_INVALID, "projection input does not fit shared memory");
+    if (smem + 1024 > e->max_dyn_smem) return fail(e, SLLM_ERR_INVALID, "projection input does not fit shared memory");
     const dim3 grid(gx, (n + nt - 1) / nt);
     int rc;
     switch (nt) {
@@ -256,7 +269,136 @@ int run_pass_t(sllm_engine* e, const PassView& pv, const int* row_tok, int n_row
     return SLLM_OK;
 }
 
+
+// ---- tensor-core path: tensor maps and launches ------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// bf16 matrix [rows][K] (K contiguous) -> map with boxes of 64 x box_rows elements, 128-byte swizzle
+int make_map(sllm_engine* e, CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    const cuuint64_t gdim[2] = {K, rows};
+    const cuuint64_t gstride[1] = {K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcBK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(e->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(e, SLLM_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    return SLLM_OK;
+}
+
+int x_map(sllm_engine* e, const void* buf, uint64_t rows_cap, uint64_t K, int bn, CUtensorMap* out) {
+    auto key = std::make_pair(buf, bn);
+    auto it = e->map_x.find(key);
+    if (it == e->map_x.end()) {
+        CUtensorMap m;
+        int rc = make_map(e, &m, buf, rows_cap, K, (uint32_t)bn);
+        if (rc) return rc;
+        it = e->map_x.emplace(key, m).first;
+    }
+    *out = it->second;
+    return SLLM_OK;
+}
+
+template <int BN, int MODE>
+int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, bool pdl) {
+    const dim3 grid((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN);
+    return launch(e, k_gemm_tc<BN, MODE>, grid, dim3(kTcThreads), tc_smem_bytes<BN>(), pdl, mw, mx, a);
+}
+
+// token-tile width: wide tiles for arithmetic intensity, narrower ones while the grid would not fill the GPU
+int pick_bn(const sllm_engine* e, int R, int n) {
+    if (n <= 32) return 32;
+    if (n <= 64) return 64;
+    const int tiles_m = (R + kTcBM - 1) / kTcBM;
+    for (int bn : {256, 128}) if (tiles_m * ((n + bn - 1) / bn) >= e->sm_count) return bn;
+    return n <= 128 ? 128 : 64;
+}
+
+template <int MODE>
+int launch_tc(sllm_engine* e, const CUtensorMap& mw, const void* xbuf, uint64_t x_rows_cap, const TcArgs& a, bool pdl) {
+    const int bn = pick_bn(e, a.R, a.n_tok);
+    CUtensorMap mx;
+    int rc = x_map(e, xbuf, x_rows_cap, (uint64_t)a.K, bn, &mx);
+    if (rc) return rc;
+    switch (bn) {
+        case 32: return launch_tc_bn<32, MODE>(e, mw, mx, a, pdl);
+        case 64: return launch_tc_bn<64, MODE>(e, mw, mx, a, pdl);
+        case 128: return launch_tc_bn<128, MODE>(e, mw, mx, a, pdl);
+        default: return launch_tc_bn<256, MODE>(e, mw, mx, a, pdl);
+    }
+}
+
+template <int MODE>
+int configure_tc(sllm_engine* e) {
+    int rc = SLLM_OK;
+    auto set = [&](auto kern, size_t bytes) {
+        if (!rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+            rc = fail(e, SLLM_ERR_CUDA, "cudaFuncSetAttribute failed for the tensor-core projection kernel");
+    };
+    set(k_gemm_tc<32, MODE>, tc_smem_bytes<32>());
+    set(k_gemm_tc<64, MODE>, tc_smem_bytes<64>());
+    set(k_gemm_tc<128, MODE>, tc_smem_bytes<128>());
+    set(k_gemm_tc<256, MODE>, tc_smem_bytes<256>());
+    return rc;
+}
+
+int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl);
+
+// The model over a pass of many tokens, bf16 weights: tcgen05 projections.
+int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    const ModelDims& m = e->md;
+    KvView kv{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    const int n = pv.n_tok;
+    TcArgs a{};
+    a.m = m; a.kv = kv; a.pass = pv; a.rope = e->rope; a.status = e->d_status; a.n_tok = n;
+    for (int l = 0; l < m.L; ++l) {
+        const LayerW& w = e->layers[l];
+        a.layer = l;
+        int rc = launch(e, k_rmsnorm_bf16, dim3(n), dim3(256), 0, pdl, (const float*)e->x, w.g_attn, e->xn16, m.D, m.eps,
+                        (const int*)nullptr, l == 0 ? (const float*)e->emb_f32 : (const float*)nullptr, pv.tok_id, e->x);
+        if (rc) return rc;
+        a.R = 3 * m.D; a.K = m.D; a.out = e->q; a.out_bf16 = nullptr;
+        rc = launch_tc<kModeQKV>(e, e->map_wqkv[l], e->xn16, e->pass_cap, a, pdl);
+        if (rc) return rc;
+        AttnDecArgs t{};
+        t.q = e->q; t.out = e->att; t.out_bf16 = e->att16; t.m = m; t.kv = kv; t.pass = pv; t.layer = l;
+        t.n_splits = 1; t.keys_per_split = e->pages_per_seq * kPage;
+        t.part_o = e->part_o; t.part_ml = e->part_ml; t.ticket = e->ticket;
+        rc = launch_attn_any(e, t, pdl);
+        if (rc) return rc;
+        a.R = m.D; a.K = m.D; a.out = e->x;
+        rc = launch_tc<kModeResidual>(e, e->map_wo[l], e->att16, e->pass_cap, a, pdl);
+        if (rc) return rc;
+        rc = launch(e, k_rmsnorm_bf16, dim3(n), dim3(256), 0, pdl, (const float*)e->x, w.g_ffn, e->xn16, m.D, m.eps,
+                    (const int*)nullptr, (const float*)nullptr, pv.tok_id, e->x);
+        if (rc) return rc;
+        a.R = 2 * m.F; a.K = m.D; a.out = nullptr; a.out_bf16 = e->hid16;
+        rc = launch_tc<kModeGateUp>(e, e->map_wgu[l], e->xn16, e->pass_cap, a, pdl);
+        if (rc) return rc;
+        a.R = m.D; a.K = m.F; a.out = e->x; a.out_bf16 = nullptr;
+        rc = launch_tc<kModeResidual>(e, e->map_wd[l], e->hid16, e->pass_cap, a, pdl);
+        if (rc) return rc;
+    }
+    if (n_rows > 0) {
+        if (n_rows > e->logit_rows_cap) return fail(e, SLLM_ERR_INVALID, "too many logits rows for one pass");
+        int rc = launch(e, k_rmsnorm_bf16, dim3(n_rows), dim3(256), 0, pdl, (const float*)e->x, (const float*)e->g_final,
+                        e->head16, m.D, m.eps, row_tok, (const float*)nullptr, pv.tok_id, e->x);
+        if (rc) return rc;
+        TcArgs h = a;
+        h.R = m.V; h.K = m.D; h.out = logits; h.out_bf16 = nullptr; h.n_tok = n_rows;
+        rc = launch_tc<kModeHead>(e, e->map_head, e->head16, e->logit_rows_cap, h, pdl);
+        if (rc) return rc;
+    }
+    return SLLM_OK;
+}
+
+int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl) { return launch_attn<__nv_bfloat16>(e, t, pdl); }
+
 int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    if (!e->f32 && e->encode_tiled && pv.n_tok >= e->tc_min_tokens) return run_pass_tc(e, pv, row_tok, n_rows, logits, pdl);
     return e->f32 ? run_pass_t<float>(e, pv, row_tok, n_rows, logits, pdl)
                   : run_pass_t<__nv_bfloat16>(e, pv, row_tok, n_rows, logits, pdl);
 }
@@ -524,6 +666,34 @@ int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32
     return SLLM_OK;
 }
 
+// Final norm + tied head for selected tokens of the pass whose residual stream sits in e->x.
+int run_head(sllm_engine* e, const PassView& pv, const int* d_row_tok, int nr, float* out) {
+    const ModelDims& m = e->md;
+    if (!e->f32 && e->encode_tiled && nr >= e->tc_min_tokens) {
+        int rc = launch(e, k_rmsnorm_bf16, dim3(nr), dim3(256), 0, false, (const float*)e->x, (const float*)e->g_final,
+                        e->head16, m.D, m.eps, d_row_tok, (const float*)nullptr, pv.tok_id, e->x);
+        if (rc) return rc;
+        TcArgs h{};
+        h.m = m; h.pass = pv; h.status = e->d_status; h.R = m.V; h.K = m.D; h.out = out; h.n_tok = nr;
+        return launch_tc<kModeHead>(e, e->map_head, e->head16, e->logit_rows_cap, h, false);
+    }
+    GemvArgs a{};
+    a.m = m; a.eps = m.eps; a.W = e->emb_w; a.R = m.V; a.K = m.D; a.in = e->x; a.gain = e->g_final;
+    a.out = out; a.n_tok = nr; a.row_tok = d_row_tok; a.pass = pv;
+    return e->f32 ? launch_gemv<float, kModeHead>(e, a, false) : launch_gemv<__nv_bfloat16, kModeHead>(e, a, false);
+}
+
+int check_status(sllm_engine* e) {
+    unsigned int st = 0;
+    CU(cudaMemcpyAsync(&st, e->d_status, sizeof st, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    if (st) {
+        CU(cudaMemsetAsync(e->d_status, 0, sizeof st, e->stream));
+        return fail(e, SLLM_ERR_DEVICE_WAIT, "a bounded device-side wait gave up (code " + std::to_string(st) + ")");
+    }
+    return SLLM_OK;
+}
+
 // Runs every prompt position through the model in chunks.  want_all: logits of every position go
 // to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
 int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits) {
@@ -544,10 +714,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         for (size_t r0 = 0; r0 < c_row.size(); r0 += e->logit_rows_cap) {
             const int nr = (int)std::min<size_t>(e->logit_rows_cap, c_row.size() - r0);
             CU(cudaMemcpyAsync(e->d_row_tok, c_row.data() + r0, nr * 4, cudaMemcpyHostToDevice, e->stream));
-            GemvArgs a{};
-            a.m = m; a.eps = m.eps; a.W = e->emb_w; a.R = m.V; a.K = m.D; a.in = e->x; a.gain = e->g_final;
-            a.out = e->pass_logits; a.n_tok = nr; a.row_tok = e->d_row_tok; a.pass = pv;
-            rc = e->f32 ? launch_gemv<float, kModeHead>(e, a, false) : launch_gemv<__nv_bfloat16, kModeHead>(e, a, false);
+            rc = run_head(e, pv, e->d_row_tok, nr, e->pass_logits);
             if (rc) return rc;
             if (host_logits) {
                 CU(cudaMemcpyAsync(host_logits + (row_base + r0) * m.V, e->pass_logits, (size_t)nr * m.V * 4,
@@ -571,7 +738,9 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         }
         off += lens[s];
     }
-    return flush();
+    int rc = flush();
+    if (rc) return rc;
+    return check_status(e);
 }
 
 }  // namespace
@@ -734,6 +903,28 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->att, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->hid, (size_t)e->pass_cap * F, &e->scratch_bytes);
     A(&e->step_logits, (size_t)e->max_batch * V, &e->scratch_bytes);
     A(&e->pass_logits, (size_t)e->logit_rows_cap * V, &e->scratch_bytes);
+    A(&e->d_status, 4, &e->scratch_bytes);
+    if (!e->f32) {
+        A(&e->xn16, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->att16, (size_t)e->pass_cap * D, &e->scratch_bytes);
+        A(&e->hid16, (size_t)e->pass_cap * F, &e->scratch_bytes); A(&e->head16, (size_t)e->logit_rows_cap * D, &e->scratch_bytes);
+        cudaDriverEntryPointQueryResult qres;
+        if (!rc && (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &e->encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
+                    qres != cudaDriverEntryPointSuccess || !e->encode_tiled)) {
+            e->err = "cuTensorMapEncodeTiled is not available from this driver"; rc = SLLM_ERR_CUDA;
+        }
+        e->map_wqkv.resize(L); e->map_wo.resize(L); e->map_wgu.resize(L); e->map_wd.resize(L);
+        for (uint64_t l = 0; l < L && !rc; ++l) {
+            rc = make_map(e, &e->map_wqkv[l], e->layers[l].wqkv, 3 * D, D, kTcBM);
+            if (!rc) rc = make_map(e, &e->map_wo[l], e->layers[l].wo, D, D, kTcBM);
+            if (!rc) rc = make_map(e, &e->map_wgu[l], e->layers[l].wgu, 2 * F, D, kTcBM);
+            if (!rc) rc = make_map(e, &e->map_wd[l], e->layers[l].wd, D, F, kTcBM);
+        }
+        if (!rc) rc = make_map(e, &e->map_head, e->emb_w, V, D, kTcBM);
+        if (!rc) rc = configure_tc<kModeQKV>(e);
+        if (!rc) rc = configure_tc<kModeResidual>(e);
+        if (!rc) rc = configure_tc<kModeGateUp>(e);
+        if (!rc) rc = configure_tc<kModeHead>(e);
+    }
     A(&e->part_o, (size_t)e->split_tok_cap * H * kMaxSplits * hd, &e->scratch_bytes);
     A(&e->part_ml, (size_t)e->split_tok_cap * H * kMaxSplits * 2, &e->scratch_bytes);
     A(&e->ticket, (size_t)e->split_tok_cap * H, &e->scratch_bytes);

