@@ -148,6 +148,17 @@ int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* pr
  * the stream is idle.  draws_dev_index selects how draws are consumed as in sllm_generate. */
 int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws);
 
+/* ---- single kernels, device pointers in and out --------------------------------------- */
+/* The flash-decode attention kernel on its own (the fused form of ops::attention for one cached
+ * query position per token, src/ops/attention.cpp:143-184): d_q [n_tok][d_model] fp32 rotated
+ * queries, d_tok_slot / d_tok_pos [n_tok] int32 (slot and position of each query; keys
+ * 0..position of that slot's KV cache are attended), d_out [n_tok][d_model] fp32.  All four are
+ * DEVICE pointers.  n_splits (1..32) blocks share each (token, head); with more than one, partial
+ * results go through scratch memory that the engine allocated at creation.  The launch is
+ * asynchronous on `stream` (a cudaStream_t as void*; NULL = the engine's stream). */
+int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_tok_slot,
+                       const int32_t* d_tok_pos, uint32_t n_splits, float* d_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

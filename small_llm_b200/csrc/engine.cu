@@ -1244,4 +1244,58 @@ int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uin
     return SLLM_OK;
 }
 
+// ---- single-kernel entry points ------------------------------------------------------------------------------
+namespace {
+
+int attn_decode_launch(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_slot,
+                       const int32_t* d_pos, uint32_t n_splits, float* d_out, cudaStream_t stream, float* part_o,
+                       float* part_ml, unsigned int* ticket) {
+    const ModelDims& m = e->md;
+    AttnDecArgs t{};
+    t.q = d_q; t.out = d_out; t.out_bf16 = nullptr; t.m = m;
+    t.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    t.pass = PassView{nullptr, d_slot, d_pos, (int)n_tok};
+    t.layer = (int)layer;
+    const int pages_per_split = (e->pages_per_seq + (int)n_splits - 1) / (int)n_splits;
+    t.keys_per_split = pages_per_split * kPage;
+    t.n_splits = (e->pages_per_seq + pages_per_split - 1) / pages_per_split;
+    t.part_o = part_o; t.part_ml = part_ml; t.ticket = ticket;
+    const dim3 grid(t.n_splits, m.H, n_tok), block(kAttnThreads);
+    void (*kern)(AttnDecArgs) = nullptr;
+    if (e->f32) {
+        switch (m.hd) { case 16: kern = k_attn_decode<float, 16>; break; case 32: kern = k_attn_decode<float, 32>; break;
+                        case 64: kern = k_attn_decode<float, 64>; break; case 128: kern = k_attn_decode<float, 128>; break; }
+    } else {
+        switch (m.hd) { case 16: kern = k_attn_decode<__nv_bfloat16, 16>; break; case 32: kern = k_attn_decode<__nv_bfloat16, 32>; break;
+                        case 64: kern = k_attn_decode<__nv_bfloat16, 64>; break; case 128: kern = k_attn_decode<__nv_bfloat16, 128>; break; }
+    }
+    if (!kern) return fail(e, SLLM_ERR_INVALID, "unsupported head_dim");
+    kern<<<grid, block, 0, stream>>>(t);
+    CU(cudaGetLastError());
+    e->launches += 1;
+    return SLLM_OK;
+}
+
+int attn_args_check(sllm_engine* e, uint32_t layer, uint32_t n_tok, const void* q, const void* s, const void* p,
+                    uint32_t n_splits, const void* out) {
+    if (!e) return SLLM_ERR_INVALID;
+    if (!q || !s || !p || !out) return fail(e, SLLM_ERR_INVALID, "attention kernel: null device pointer");
+    if (layer >= (uint32_t)e->md.L) return fail(e, SLLM_ERR_INVALID, "attention kernel: layer out of range");
+    if (n_tok == 0) return fail(e, SLLM_ERR_INVALID, "attention kernel: no tokens");
+    if (n_splits < 1 || n_splits > (uint32_t)kMaxSplits) return fail(e, SLLM_ERR_INVALID, "attention kernel: n_splits must be 1..32");
+    return SLLM_OK;
+}
+
+}  // namespace
+
+int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_tok_slot,
+                       const int32_t* d_tok_pos, uint32_t n_splits, float* d_out, void* stream) {
+    int rc = attn_args_check(e, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out);
+    if (rc) return rc;
+    if (n_splits > 1 && n_tok > (uint32_t)e->split_tok_cap)
+        return fail(e, SLLM_ERR_CAPACITY, "attention kernel: more than 64 tokens need n_splits = 1");
+    return attn_decode_launch(e, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out,
+                              stream ? (cudaStream_t)stream : e->stream, e->part_o, e->part_ml, e->ticket);
+}
+
 }  // extern "C"

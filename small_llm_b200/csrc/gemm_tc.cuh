@@ -22,7 +22,7 @@ namespace sllm {
 constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
 constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int kTcThreads = 192;
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // a wait gives up after two seconds
 
 struct TcArgs {
     int R, K, n_tok;
@@ -52,9 +52,15 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // bounded wait; false = gave up (status word raised)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int code) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try(bar, parity)) return true;
-        if (i > 64) __nanosleep(128);
+        if (i < 64) continue;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) break;
+        __nanosleep(128);
     }
     atomicExch(status, code);
     return false;
