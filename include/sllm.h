@@ -159,6 +159,24 @@ int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt,
 int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_tok_slot,
                        const int32_t* d_tok_pos, uint32_t n_splits, float* d_out, void* stream);
 
+/* No counterpart in the reference.  Same kernel, same arguments and same results as
+ * sllm_k_attn_decode, for callers that must not allocate device memory or cannot rely on memory
+ * obtained from cudaMalloc: a serving process that has handed the whole device to its own pool
+ * allocator (so a later cudaMalloc may fail), or a latency-critical decode thread that cannot
+ * afford the device-wide synchronisation cudaMalloc / cudaFree may imply.  The split-K scratch
+ * lives in a fixed array inside the library's device image (about 1.1 MB, resident on every GPU
+ * that loads the library until the process exits) instead of in allocated memory, and the call
+ * performs no cudaMalloc, cudaFree or other allocating routine.
+ * Limits: n_tok * num_heads <= 64, n_splits <= 32, head_dim <= 128; larger requests are refused
+ * with SLLM_ERR_CAPACITY.  The engine's device must be the current device.
+ * The first call on a device looks up the array's device address (once per device); make that
+ * first call outside any stream capture.  All calls share the one array: it keeps the previous
+ * call's contents (the entry point clears the part that must start at zero), and two calls whose
+ * kernels overlap on the GPU -- different streams, or different engines on one GPU -- race. */
+int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q,
+                              const int32_t* d_tok_slot, const int32_t* d_tok_pos, uint32_t n_splits, float* d_out,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

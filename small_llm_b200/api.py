@@ -67,7 +67,7 @@ ABI_SYMBOLS = [
     "sllm_engine_create", "sllm_engine_destroy", "sllm_engine_stats", "sllm_engine_stream", "sllm_num_params",
     "sllm_param_info", "sllm_set_param", "sllm_load_checkpoint", "sllm_forward_logits", "sllm_reset",
     "sllm_prefill", "sllm_sample", "sllm_decode_step", "sllm_get_step_logits", "sllm_get_tokens",
-    "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode",
+    "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
 ]
 
 
@@ -111,7 +111,7 @@ def load_library(path: str | None = None):
                                   C.c_uint64, u64p]
     lib.sllm_decode_loop.argtypes = [E, C.c_uint64, C.POINTER(_Sampling), f64p]
     i32p = C.POINTER(C.c_int32)
-    for fn in (lib.sllm_k_attn_decode,):
+    for fn in (lib.sllm_k_attn_decode, lib.sllm_k_attn_decode_static):
         fn.argtypes = [E, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     if path is None:
         _LIB = lib
@@ -311,9 +311,9 @@ class Engine:
         return [out[i, : int(out_lens[i])].copy() for i in range(n)]
 
     def k_attn_decode(self, layer: int, n_tok: int, d_q: int, d_tok_slot: int, d_tok_pos: int, n_splits: int,
-                      d_out: int, stream: int = 0):
+                      d_out: int, stream: int = 0, static_scratch: bool = False):
         """Launches the flash-decode attention kernel alone; every d_* is a device address."""
-        fn = self.lib.sllm_k_attn_decode
+        fn = self.lib.sllm_k_attn_decode_static if static_scratch else self.lib.sllm_k_attn_decode
         self._ck(fn(self.h, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out, stream or None))
 
     def stats(self) -> dict:

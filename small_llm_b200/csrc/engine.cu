@@ -1247,6 +1247,17 @@ int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uin
 // ---- single-kernel entry points ------------------------------------------------------------------------------
 namespace {
 
+// Scratch of sllm_k_attn_decode_static: tickets | (max, sum) pairs | partial outputs.
+constexpr int kStaticPairs = 64;                     // n_tok * heads
+constexpr int kStaticHd = 128;
+constexpr size_t kStaticTicketBytes = 256;           // 64 x u32
+constexpr size_t kStaticMlBytes = (size_t)kStaticPairs * kMaxSplits * 2 * sizeof(float);
+constexpr size_t kStaticOBytes = (size_t)kStaticPairs * kMaxSplits * kStaticHd * sizeof(float);
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticTicketBytes + kStaticMlBytes + kStaticOBytes];
+
+// device address of the array per device ordinal, looked up once with that device current
+unsigned char* g_static_scratch_addr[64] = {};
+
 int attn_decode_launch(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_slot,
                        const int32_t* d_pos, uint32_t n_splits, float* d_out, cudaStream_t stream, float* part_o,
                        float* part_ml, unsigned int* ticket) {
@@ -1296,6 +1307,37 @@ int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const flo
         return fail(e, SLLM_ERR_CAPACITY, "attention kernel: more than 64 tokens need n_splits = 1");
     return attn_decode_launch(e, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out,
                               stream ? (cudaStream_t)stream : e->stream, e->part_o, e->part_ml, e->ticket);
+}
+
+// Allocation-free variant: split-K scratch in the library's own device array (see sllm.h).
+int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q,
+                              const int32_t* d_tok_slot, const int32_t* d_tok_pos, uint32_t n_splits, float* d_out,
+                              void* stream) {
+    int rc = attn_args_check(e, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out);
+    if (rc) return rc;
+    if ((uint64_t)n_tok * (uint64_t)e->md.H > (uint64_t)kStaticPairs || e->md.hd > kStaticHd)
+        return fail(e, SLLM_ERR_CAPACITY, "sllm_k_attn_decode_static: request exceeds the fixed scratch (n_tok * num_heads <= 64, "
+                                           "head_dim <= 128); use sllm_k_attn_decode");
+    int cur = -1;
+    CU(cudaGetDevice(&cur));
+    if (cur != e->dev || cur < 0 || cur >= 64)
+        return fail(e, SLLM_ERR_STATE, "sllm_k_attn_decode_static: the engine's device must be the current device");
+    if (!g_static_scratch_addr[cur]) {
+        // The array's name is only a host-side handle: the kernel needs the address the symbol has on
+        // THIS device, which the runtime reports once the device is current.
+        void* p = nullptr;
+        CU(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+        if (!p) return fail(e, SLLM_ERR_CUDA, "sllm_k_attn_decode_static: no device address for the scratch array");
+        g_static_scratch_addr[cur] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_static_scratch_addr[cur];
+    cudaStream_t st = stream ? (cudaStream_t)stream : e->stream;
+    // tickets must start at zero; partial results are fully rewritten before they are read
+    CU(cudaMemsetAsync(base, 0, kStaticTicketBytes, st));
+    return attn_decode_launch(e, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out, st,
+                              reinterpret_cast<float*>(base + kStaticTicketBytes + kStaticMlBytes),
+                              reinterpret_cast<float*>(base + kStaticTicketBytes),
+                              reinterpret_cast<unsigned int*>(base));
 }
 
 }  // extern "C"
