@@ -50,8 +50,8 @@ __global__ void __launch_bounds__(kAttnThreads) k_attn_decode(const AttnDecArgs 
     const int split = blockIdx.x, head = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    pdl_launch_dependents();        // successors may start fetching their weights now
     pdl_wait();
-    pdl_launch_dependents();
 
     const int pos = a.pass.tok_pos[tok];
     const int slot = a.pass.tok_slot[tok];

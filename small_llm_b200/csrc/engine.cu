@@ -184,6 +184,16 @@ int opt_in_smem(sllm_engine* e, K kern) {
 }
 
 // ---- projections ---------------------------------------------------------------------------------------
+template <typename WT, int MODE, int PF>
+int launch_gemv_pf(sllm_engine* e, const GemvArgs& a, bool pdl, int nt, dim3 grid, size_t smem) {
+    switch (nt) {
+        case 1: return launch(e, k_gemv<WT, 1, MODE, PF>, grid, dim3(kGemvThreads), smem, pdl, a);
+        case 2: return launch(e, k_gemv<WT, 2, MODE, PF>, grid, dim3(kGemvThreads), smem, pdl, a);
+        case 4: return launch(e, k_gemv<WT, 4, MODE, PF>, grid, dim3(kGemvThreads), smem, pdl, a);
+        default: return launch(e, k_gemv<WT, 8, MODE, PF>, grid, dim3(kGemvThreads), smem, pdl, a);
+    }
+}
+
 template <typename WT, int MODE>
 int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
     const int groups = a.R / 2;
@@ -193,17 +203,10 @@ int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
     const size_t smem = (size_t)nt * a.K * sizeof(float);
     if (smem + 1024 > e->max_dyn_smem) return fail(e, SLLM_ERR_INVALID, "projection input does not fit shared memory");
     const dim3 grid(gx, (n + nt - 1) / nt);
-    int rc;
-    switch (nt) {
-        case 1: rc = set_smem(e, k_gemv<WT, 1, MODE>, smem); if (rc) return rc;
-                return launch(e, k_gemv<WT, 1, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
-        case 2: rc = set_smem(e, k_gemv<WT, 2, MODE>, smem); if (rc) return rc;
-                return launch(e, k_gemv<WT, 2, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
-        case 4: rc = set_smem(e, k_gemv<WT, 4, MODE>, smem); if (rc) return rc;
-                return launch(e, k_gemv<WT, 4, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
-        default: rc = set_smem(e, k_gemv<WT, 8, MODE>, smem); if (rc) return rc;
-                return launch(e, k_gemv<WT, 8, MODE>, grid, dim3(kGemvThreads), smem, pdl, a);
-    }
+    // register prefetch depth: 3 chunks per lane cover K = 640 in bf16, 7 cover K = 1728
+    const int chunks_per_lane = (a.K / Elems<WT>::per16 + 31) / 32;
+    if (chunks_per_lane > 3) return launch_gemv_pf<WT, MODE, 7>(e, a, pdl, nt, grid, smem);
+    return launch_gemv_pf<WT, MODE, 3>(e, a, pdl, nt, grid, smem);
 }
 
 template <typename KVT>
@@ -405,10 +408,14 @@ int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows,
 
 template <typename WT, int MODE>
 int configure_gemv(sllm_engine* e) {
-    int rc = opt_in_smem(e, k_gemv<WT, 1, MODE>);
-    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 2, MODE>);
-    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 4, MODE>);
-    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 8, MODE>);
+    int rc = opt_in_smem(e, k_gemv<WT, 1, MODE, 3>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 2, MODE, 3>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 4, MODE, 3>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 8, MODE, 3>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 1, MODE, 7>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 2, MODE, 7>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 4, MODE, 7>);
+    if (!rc) rc = opt_in_smem(e, k_gemv<WT, 8, MODE, 7>);
     return rc;
 }
 template <typename WT>

@@ -43,7 +43,9 @@ struct GemvArgs {
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
 
-template <typename WT, int NT, int MODE>
+// PF = 16-byte chunks per lane and row that are fetched into registers BEFORE the kernel waits for its
+// predecessor (weights never change during a pass, so this overlaps the predecessor's tail).
+template <typename WT, int NT, int MODE, int PF>
 __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
     constexpr int EPC = Elems<WT>::per16;
     constexpr int RPW = 2;
@@ -57,8 +59,24 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
     const int nt = min(NT, a.n_tok - t0);
     constexpr bool kNorm = (MODE != kModeResidual);
 
-    pdl_wait();
+    // ---- weights of this warp's first row pair: in flight before anything else -------------------
+    const int nchunk = K / EPC;
+    const int groups = a.R / RPW;
+    const int gw = blockIdx.x * kGemvWarps + warp;
+    const int gstride = gridDim.x * kGemvWarps;
+    const WT* Wt = reinterpret_cast<const WT*>(a.W);
     pdl_launch_dependents();
+    uint4 pf0[PF], pf1[PF];
+    if (gw < groups) {
+        const uint4* w0 = reinterpret_cast<const uint4*>(Wt + (size_t)(gw * RPW) * K);
+        const uint4* w1 = reinterpret_cast<const uint4*>(Wt + (size_t)(gw * RPW + 1) * K);
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int c = lane + 32 * i;
+            if (c < nchunk) { pf0[i] = ldg_stream(w0 + c); pf1[i] = ldg_stream(w1 + c); }
+        }
+    }
+    pdl_wait();
 
     // ---- prologue: activations to shared memory (+ RMSNorm) ---------------------------------
 #pragma unroll
@@ -101,12 +119,6 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
     }
 
     // ---- stream the rows -------------------------------------------------------------------
-    const int nchunk = K / EPC;
-    const int groups = a.R / RPW;
-    const int gw = blockIdx.x * kGemvWarps + warp;
-    const int gstride = gridDim.x * kGemvWarps;
-    const WT* Wt = reinterpret_cast<const WT*>(a.W);
-
     for (int g = gw; g < groups; g += gstride) {
         const int r = g * RPW;
         const uint4* w0 = reinterpret_cast<const uint4*>(Wt + (size_t)r * K);
@@ -114,10 +126,7 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
         float acc0[NT], acc1[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) { acc0[t] = 0.f; acc1[t] = 0.f; }
-#pragma unroll 4
-        for (int c = lane; c < nchunk; c += 32) {
-            const uint4 v0 = ldg_stream(w0 + c);
-            const uint4 v1 = ldg_stream(w1 + c);
+        auto fma_chunk = [&](const uint4& v0, const uint4& v1, int c) {
             float f0[EPC], f1[EPC];
             unpack16<WT>(v0, f0);
             unpack16<WT>(v1, f1);
@@ -131,6 +140,21 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
                     acc1[t] += f1[e] * x4.x + f1[e + 1] * x4.y + f1[e + 2] * x4.z + f1[e + 3] * x4.w;
                 }
             }
+        };
+        int c_begin = lane;
+        if (g == gw) {                       // first pair: the prefetched chunks
+#pragma unroll
+            for (int i = 0; i < PF; ++i) {
+                const int c = lane + 32 * i;
+                if (c < nchunk) fma_chunk(pf0[i], pf1[i], c);
+            }
+            c_begin = lane + 32 * PF;
+        }
+#pragma unroll 4
+        for (int c = c_begin; c < nchunk; c += 32) {
+            const uint4 v0 = ldg_stream(w0 + c);
+            const uint4 v1 = ldg_stream(w1 + c);
+            fma_chunk(v0, v1, c);
         }
 #pragma unroll
         for (int t = 0; t < NT; ++t) { acc0[t] = warp_sum(acc0[t]); acc1[t] = warp_sum(acc1[t]); }

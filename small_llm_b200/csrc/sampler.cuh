@@ -9,8 +9,10 @@
 // No sort is performed.  Probability mass is held as 64-bit fixed point (weight * 2^47, exact for
 // every weight >= 2^-24), so partial sums are associative and the result is independent of the
 // order in which threads add.  "The element at which the descending cumulative mass first reaches
-// a target" is found by bucket refinement over the weights' float bit patterns: <= 4 histogram
-// passes of 1024 buckets, then ties (equal weights) are resolved towards the lower id.
+// a target" is found by bucket refinement over the weights' float bit patterns: a 1024-bucket
+// histogram of the whole key range (built once, while the weights are computed, and shared by both
+// queries), then <= 2 narrower histograms per query; ties (equal weights) go to the lower id.
+// Histogram mass is accumulated as three 16-bit limbs in 32-bit shared-memory atomics.
 #pragma once
 #include "common.cuh"
 
@@ -47,94 +49,128 @@ struct SampleArgs {
     int* next_tok_slot;
 };
 
-struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned int cnt_above, ties, r; int found; };
-
+// weight in [0,1] -> floor(weight * 2^47), by integer arithmetic on the float's bits
 __device__ __forceinline__ unsigned long long fix_of(float w) {
-    return (unsigned long long)((double)w * (double)(1ull << kFixShift));
+    const uint32_t b = __float_as_uint(w);
+    const int e = (int)(b >> 23);
+    if (e == 0) return 0ull;                                   // denormals are below 2^-47
+    const unsigned long long man = (unsigned long long)((b & 0x7fffffu) | 0x800000u);
+    const int sh = e - 150 + kFixShift;                        // value = man * 2^(e-150)
+    if (sh >= 0) return man << sh;
+    return sh > -24 ? (man >> (-sh)) : 0ull;
 }
 
-// Finds the element, in descending (key, then ascending id) order, at which the running mass
-// first reaches `target`.  All threads of the block call it with the same arguments.
-__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t kmin, uint32_t kmax,
-                                    unsigned long long* h_mass, unsigned int* h_cnt, int* s_pick) {
+struct SampHist {                 // shared-memory histogram: mass as 16-bit limbs, plus counts
+    unsigned int l0[kSampBuckets], l1[kSampBuckets], l2[kSampBuckets], cnt[kSampBuckets];
+};
+__device__ __forceinline__ void hist_add(SampHist& h, int b, unsigned long long q) {
+    atomicAdd(&h.l0[b], (unsigned int)(q & 0xffffu));
+    atomicAdd(&h.l1[b], (unsigned int)((q >> 16) & 0xffffu));
+    atomicAdd(&h.l2[b], (unsigned int)(q >> 32));              // <= 2^15 per element
+    atomicAdd(&h.cnt[b], 1u);
+}
+__device__ __forceinline__ unsigned long long hist_mass(const SampHist& h, int b) {
+    return (unsigned long long)h.l0[b] + ((unsigned long long)h.l1[b] << 16) + ((unsigned long long)h.l2[b] << 32);
+}
+__device__ __forceinline__ void hist_clear(SampHist& h) {
+    for (int b = threadIdx.x; b < kSampBuckets; b += kSampThreads) { h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; h.cnt[b] = 0; }
+}
+__device__ __forceinline__ int shift_for(uint32_t width) {
+    int sh = 0;
+    while ((width >> sh) >= (uint32_t)kSampBuckets) ++sh;
+    return sh;
+}
+
+struct SampScratch {
+    unsigned long long sc_m[32];
+    unsigned int sc_c[32];
+    unsigned long long pk_above_m, pk_m, tot_m;
+    unsigned int pk_above_c, pk_c, tot_c;
+    int pick;
+};
+
+struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned int cnt_above, ties, r; int found; };
+
+// Scans histogram h (keys lo..hi, bucket = (key-lo)>>sh) from the highest bucket down and picks the first
+// non-empty bucket at which cum + running mass reaches target.  Returns false when none does; then cum / cnt
+// have absorbed the whole range.  On success lo/hi shrink to the picked bucket and cum / cnt count what lies above.
+__device__ bool scan_pick(const SampHist& h, SampScratch& s, unsigned long long target, uint32_t& lo, uint32_t& hi, int sh,
+                          unsigned long long& cum, unsigned int& cnt, unsigned long long& bucket_mass, unsigned int& bucket_cnt) {
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int top = (int)((hi - lo) >> sh);
+    const int b = top - tid;
+    unsigned long long my_m = 0; unsigned int my_c = 0;
+    if (b >= 0) { my_m = hist_mass(h, b); my_c = h.cnt[b]; }
+    unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long m2 = __shfl_up_sync(0xffffffffu, inc_m, o);
+        const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc_c, o);
+        if (lane >= o) { inc_m += m2; inc_c += c2; }
+    }
+    if (tid == 0) s.pick = kSampBuckets;
+    if (lane == 31) { s.sc_m[wp] = inc_m; s.sc_c[wp] = inc_c; }
+    __syncthreads();
+    unsigned long long off_m = 0; unsigned int off_c = 0;
+    for (int k = 0; k < wp; ++k) { off_m += s.sc_m[k]; off_c += s.sc_c[k]; }
+    inc_m += off_m; inc_c += off_c;
+    if (b >= 0 && my_c > 0 && cum + inc_m >= target) atomicMin(&s.pick, tid);
+    if (tid == kSampThreads - 1) { s.tot_m = inc_m; s.tot_c = inc_c; }
+    __syncthreads();
+    const int pick = s.pick;
+    if (pick == kSampBuckets) {
+        cum += s.tot_m; cnt += s.tot_c;
+        __syncthreads();
+        return false;
+    }
+    if (tid == pick) { s.pk_above_m = inc_m - my_m; s.pk_above_c = inc_c - my_c; s.pk_m = my_m; s.pk_c = my_c; }
+    __syncthreads();
+    cum += s.pk_above_m; cnt += s.pk_above_c;
+    bucket_mass = s.pk_m; bucket_cnt = s.pk_c;
+    const uint32_t nlo = lo + ((uint32_t)(top - pick) << sh);
+    uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
+    if (nhi > hi) nhi = hi;
+    lo = nlo; hi = nhi;
+    __syncthreads();
+    return true;
+}
+
+// Finds the element, in descending (key, then ascending id) order, at which the running mass first reaches
+// `target`.  h0 is the histogram of the whole range [kmin, kmax] with shift sh0; h1 is working space.
+__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t kmin, uint32_t kmax, int sh0,
+                                    const SampHist& h0, SampHist& h1, SampScratch& s) {
     const int tid = threadIdx.x;
     uint32_t lo = kmin, hi = kmax;
-    unsigned long long cum = 0;      // mass of keys > hi
-    unsigned int cnt = 0;            // elements with key > hi
+    unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
     SelectResult res;
-    res.found = 0;
+    res.found = 0; res.qk = 0; res.ties = 0; res.r = 0;
+    int sh = sh0;
     for (int pass = 0; pass < 5; ++pass) {
-        const uint32_t width = hi - lo;              // inclusive range has width+1 keys
-        int sh = 0;
-        while ((width >> sh) >= (uint32_t)kSampBuckets) ++sh;
-        for (int b = tid; b < kSampBuckets; b += kSampThreads) { h_mass[b] = 0; h_cnt[b] = 0; }
-        if (tid == 0) *s_pick = kSampBuckets;
-        __syncthreads();
-        for (int i = tid; i < V; i += kSampThreads) {
-            const uint32_t key = __float_as_uint(w[i]);
-            if (key >= lo && key <= hi) {
-                const int b = (int)((key - lo) >> sh);
-                atomicAdd(&h_mass[b], fix_of(w[i]));
-                atomicAdd(&h_cnt[b], 1u);
+        const SampHist* h = &h0;
+        if (pass > 0) {
+            sh = shift_for(hi - lo);
+            hist_clear(h1);
+            __syncthreads();
+            for (int i = tid; i < V; i += kSampThreads) {
+                const uint32_t key = __float_as_uint(w[i]);
+                if (key >= lo && key <= hi) hist_add(h1, (int)((key - lo) >> sh), fix_of(w[i]));
             }
-        }
-        __syncthreads();
-        // thread j looks at bucket (top - j): descending order; block-wide inclusive scan
-        const int top = (int)(width >> sh);
-        __shared__ unsigned long long sc_m[32];
-        __shared__ unsigned int sc_c[32];
-        unsigned long long my_m = 0; unsigned int my_c = 0;
-        const int b = top - tid;
-        if (b >= 0) { my_m = h_mass[b]; my_c = h_cnt[b]; }
-        unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
-        const int lane = tid & 31, wp = tid >> 5;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned long long m2 = __shfl_up_sync(0xffffffffu, inc_m, o);
-            const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc_c, o);
-            if (lane >= o) { inc_m += m2; inc_c += c2; }
-        }
-        if (lane == 31) { sc_m[wp] = inc_m; sc_c[wp] = inc_c; }
-        __syncthreads();
-        unsigned long long off_m = 0; unsigned int off_c = 0;
-        for (int k = 0; k < wp; ++k) { off_m += sc_m[k]; off_c += sc_c[k]; }
-        inc_m += off_m; inc_c += off_c;
-        if (b >= 0 && my_c > 0 && cum + inc_m >= target) atomicMin(s_pick, tid);
-        __syncthreads();
-        const int pick = *s_pick;
-        if (pick == kSampBuckets) {           // target beyond all the mass in range
-            res.found = 0; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.qk = 0; res.ties = 0; res.r = 0;
-            // report totals of the whole range as "above"
-            __shared__ unsigned long long tot_m; __shared__ unsigned int tot_c;
-            if (tid == kSampThreads - 1) { tot_m = inc_m; tot_c = inc_c; }
             __syncthreads();
-            res.cum_above = cum + tot_m; res.cnt_above = cnt + tot_c;
-            __syncthreads();
-            return res;
+            h = &h1;
         }
-        __shared__ unsigned long long pk_m, pk_em; __shared__ unsigned int pk_c, pk_ec;
-        if (tid == pick) { pk_m = inc_m - my_m; pk_c = inc_c - my_c; pk_em = my_m; pk_ec = my_c; }
-        __syncthreads();
-        cum += pk_m; cnt += pk_c;
-        const int pb = top - pick;
-        const uint32_t nlo = lo + ((uint32_t)pb << sh);
-        uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
-        if (nhi > hi) nhi = hi;
-        const unsigned long long em = pk_em; const unsigned int ec = pk_ec;
-        __syncthreads();
-        lo = nlo; hi = nhi;
+        if (!scan_pick(*h, s, target, lo, hi, sh, cum, cnt, bm, bc)) break;
         if (sh == 0) {                       // one key per bucket: done
-            res.found = 1; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.ties = ec;
-            res.qk = em / ec;
-            unsigned long long need = target > cum ? target - cum : 0;
+            res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
+            const unsigned long long need = target > cum ? target - cum : 0;
             unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
             if (r < 1) r = 1;
-            if (r > ec) r = ec;
+            if (r > bc) r = bc;
             res.r = (unsigned int)r;
-            return res;
+            break;
         }
     }
-    res.found = 0; res.key = lo; res.cum_above = cum; res.cnt_above = cnt; res.qk = 0; res.ties = 0; res.r = 0;
+    res.cum_above = cum; res.cnt_above = cnt;
+    if (!res.found) res.key = lo;
     return res;
 }
 
@@ -145,7 +181,6 @@ __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r,
     const int b = tid * per, e = min(V, b + per);
     unsigned int c = 0;
     for (int i = b; i < e; ++i) c += (__float_as_uint(w[i]) == key);
-    // exclusive scan of c over threads
     unsigned int inc = c;
     const int lane = tid & 31, wp = tid >> 5;
 #pragma unroll
@@ -172,22 +207,22 @@ __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r,
 
 __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
     extern __shared__ __align__(16) float w[];                 // [V] scores, then weights
-    __shared__ unsigned long long h_mass[kSampBuckets];
-    __shared__ unsigned int h_cnt[kSampBuckets];
+    __shared__ SampHist h0, h1;
+    __shared__ SampScratch sc;
     __shared__ float r_val[32];
     __shared__ int r_idx[32];
     __shared__ unsigned long long r_sum[32];
     __shared__ uint32_t r_kmin[32];
     __shared__ unsigned int s_scan[32];
-    __shared__ int s_pick, s_out;
+    __shared__ int s_out;
     __shared__ float s_max; __shared__ int s_arg;
     __shared__ unsigned long long s_total; __shared__ uint32_t s_kmin;
 
     const int slot = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int V = a.V;
 
+    pdl_launch_dependents();        // successors may start fetching their weights now
     pdl_wait();
-    pdl_launch_dependents();
 
     int n_tok = a.st.n_tok[slot];
     const int fin = a.st.finished[slot];
@@ -243,6 +278,7 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
                 kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
             }
             if (lane == 0) { r_sum[wp] = sum; r_kmin[wp] = kmin; }
+            hist_clear(h0);
             __syncthreads();
             if (tid == 0) {
                 unsigned long long t = 0; uint32_t k = 0xffffffffu;
@@ -251,11 +287,19 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
             }
             __syncthreads();
             const unsigned long long total = s_total;
+            const uint32_t klo = s_kmin;
             const uint32_t kmax = __float_as_uint(1.0f);      // the maximum's weight is exp(0) = 1
+            // histogram of the whole key range, used by both queries
+            const int sh0 = shift_for(kmax - klo);
+            for (int i = tid; i < V; i += kSampThreads) {
+                const float e = w[i];
+                hist_add(h0, (int)((__float_as_uint(e) - klo) >> sh0), fix_of(e));
+            }
+            __syncthreads();
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
-            SelectResult cut = select_mass(w, V, t1, s_kmin, kmax, h_mass, h_cnt, &s_pick);
+            const SelectResult cut = select_mass(w, V, t1, klo, kmax, sh0, h0, h1, sc);
             unsigned long long kept_mass; unsigned int kept;
             if (cut.found) { kept_mass = cut.cum_above + (unsigned long long)cut.r * cut.qk; kept = cut.cnt_above + cut.r; }
             else { kept_mass = cut.cum_above; kept = cut.cnt_above; }
@@ -264,11 +308,11 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
             if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
-            SelectResult hit = select_mass(w, V, t2, s_kmin, kmax, h_mass, h_cnt, &s_pick);
+            const SelectResult hit = select_mass(w, V, t2, klo, kmax, sh0, h0, h1, sc);
             uint32_t key; unsigned int r;
             if (hit.found && (hit.cnt_above + hit.r) <= kept) { key = hit.key; r = hit.r; }
             else if (cut.found) { key = cut.key; r = cut.r; }                  // last kept candidate
-            else { key = s_kmin; r = 0xffffffffu; }
+            else { key = klo; r = 0xffffffffu; }
             if (r == 0xffffffffu) {                                            // last of everything: highest id of the smallest key
                 unsigned int c = 0;
                 for (int i = tid; i < V; i += kSampThreads) c += (__float_as_uint(w[i]) == key);
