@@ -1,0 +1,387 @@
+// Decode step for ONE new token: each transformer layer as two thread-block-cluster kernels.
+//
+// At batch 1 every projection is a latency problem, not a bandwidth problem: the weights of a
+// layer (9.9 MB) stream in ~1.5 us, but a chain of kernels that each wait for the previous one's
+// result costs several microseconds per link.  So the links are cut from five per layer to two,
+// dependencies that stay inside one attention head or one slice of the FFN are resolved inside a
+// cluster of 8 blocks through distributed shared memory, and every block fetches its weights into
+// registers BEFORE it waits for its predecessor (griddepcontrol.wait).
+//
+//   k_attn_block  grid (8, H), cluster = the 8 blocks of a head.  x = x_in + sum(partials of the
+//                 previous FFN), RMSNorm, this head's 3*hd rows of the QKV projection (hd/8 rows of
+//                 each per block), RoPE, K/V appended to the paged cache and exchanged through DSMEM,
+//                 attention over the cached keys with the pages dealt round-robin to the 8 blocks,
+//                 partial (max, sum, out) exchanged through DSMEM and merged in rank order, then the
+//                 head's share of the out-projection: partial[h][n] = sum_d att[d] * Wo[n][h*hd + d].
+//   k_ffn_block   grid (nB), clusters of 8.  x = x_in + sum over heads of partial[h], RMSNorm, gate/up
+//                 rows of this block's hidden units, SiLU(gate)*up, their share of the down-projection,
+//                 summed over the cluster through DSMEM in rank order: partial[cluster][n].
+// The residual stream is the sum "x + partials" in a fixed order, so results do not depend on timing.
+// Same reference arithmetic as gemv.cuh / attn_decode.cuh (see the citations there).
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace sllm {
+namespace cg = cooperative_groups;
+
+constexpr int kFusedThreads = 384;
+constexpr int kFusedWarps = kFusedThreads / 32;
+constexpr int kCS = 8;                       // blocks per cluster
+
+struct FusedArgs {
+    ModelDims m;
+    KvView kv;
+    int layer;
+    const uint32_t* tok_id;                  // the pass holds one token: index 0
+    const int* tok_slot;
+    const int* tok_pos;
+    const float* x_in;                       // [D] residual before the partial sums
+    const float* parts_in;                   // [n_parts_in][D]
+    int n_parts_in;
+    float* x_out;                            // [D] residual after the partial sums (written by one block)
+    const float* gain;                       // [D]
+    const void* w1;                          // attention: wqkv [3D][D];  FFN: wgu [2F][D]
+    const void* w2;                          // attention: wo [D][D];     FFN: down weights as [F][D]
+    float* parts_out;                        // attention: [H][D];        FFN: [gridDim.x / 8][D]
+    const float2* rope;
+    const float* emb;                        // layer 0: the token's row replaces x_in
+    int upc;                                 // FFN: hidden units per block
+};
+
+// x = x_in (+ partial sums), stored as the new residual by the designated block; xs = RMSNorm(x) * gain.
+__device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, float* red, bool store) {
+    const int D = a.m.D, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* base = a.emb ? a.emb + (size_t)a.tok_id[0] * D : a.x_in;
+    float ss = 0.f;
+    for (int k = tid; k < D; k += kFusedThreads) {
+        float v = base[k];
+        for (int p = 0; p < a.n_parts_in; ++p) v += __ldcg(a.parts_in + (size_t)p * D + k);
+        xs[k] = v;
+        ss += v * v;
+        if (store) a.x_out[k] = v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kFusedWarps; ++w) s += red[w];
+    const float inv = 1.0f / sqrtf(s / (float)D + a.m.eps);
+    for (int k = tid; k < D; k += kFusedThreads) xs[k] = xs[k] * inv * a.gain[k];
+    __syncthreads();
+}
+
+// dot products of two adjacent weight rows with xs; PF chunks per lane come prefetched
+template <typename WT, int PF>
+__device__ __forceinline__ void pair_dot(const WT* w0p, const WT* w1p, const uint4* pf0, const uint4* pf1, bool prefetched,
+                                         const float* xs, int K, float& r0, float& r1) {
+    constexpr int EPC = Elems<WT>::per16;
+    const int lane = threadIdx.x & 31, nchunk = K / EPC;
+    const uint4* w0 = reinterpret_cast<const uint4*>(w0p);
+    const uint4* w1 = reinterpret_cast<const uint4*>(w1p);
+    float a0 = 0.f, a1 = 0.f;
+    auto fma_chunk = [&](const uint4& v0, const uint4& v1, int c) {
+        float f0[EPC], f1[EPC];
+        unpack16<WT>(v0, f0);
+        unpack16<WT>(v1, f1);
+#pragma unroll
+        for (int e = 0; e < EPC; e += 4) {
+            const float4 x4 = *reinterpret_cast<const float4*>(xs + c * EPC + e);
+            a0 += f0[e] * x4.x + f0[e + 1] * x4.y + f0[e + 2] * x4.z + f0[e + 3] * x4.w;
+            a1 += f1[e] * x4.x + f1[e + 1] * x4.y + f1[e + 2] * x4.z + f1[e + 3] * x4.w;
+        }
+    };
+    int c_begin = lane;
+    if (prefetched) {
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int c = lane + 32 * i;
+            if (c < nchunk) fma_chunk(pf0[i], pf1[i], c);
+        }
+        c_begin = lane + 32 * PF;
+    }
+#pragma unroll 2
+    for (int c = c_begin; c < nchunk; c += 32) fma_chunk(ldg_stream(w0 + c), ldg_stream(w1 + c), c);
+    r0 = warp_sum(a0);
+    r1 = warp_sum(a1);
+}
+
+template <typename WT, int HD, int PF>
+__global__ void __launch_bounds__(kFusedThreads) k_attn_block(const FusedArgs a) {
+    constexpr int EPC = Elems<WT>::per16;
+    constexpr int RP = HD / kCS;                 // rows of q (and of k, of v) per block
+    constexpr int NP = 3 * RP / 2;               // row pairs per block
+    constexpr int LPK = HD / EPC;                // lanes per key row / per Wo row slice
+    constexpr int KPI = 32 / LPK;
+    constexpr int DP = HD / 2;
+    constexpr int KG = kFusedThreads / DP;
+    static_assert(RP >= 2 && RP % 2 == 0, "head_dim must give each block whole RoPE pairs");
+    static_assert(kFusedThreads % DP == 0 && LPK <= 32, "unsupported head_dim");
+
+    extern __shared__ __align__(16) float xs[];          // [D]
+    __shared__ float red[kFusedWarps];
+    __shared__ float s_q[HD], s_k[HD], s_v[HD];          // filled by all 8 blocks of the head
+    __shared__ float s_part[kCS][HD + 2];                // (out[HD], max, sum) of every block
+    __shared__ float s_att[HD];
+    __shared__ float sc[kPage];
+    __shared__ float red_o[KG][HD];
+    __shared__ float red_l[KG];
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int c = (int)cluster.block_rank();
+    const int head = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int D = a.m.D;
+    const WT* W1 = reinterpret_cast<const WT*>(a.w1);
+    const WT* W2 = reinterpret_cast<const WT*>(a.w2);
+
+    // ---- before the dependency wait: weights into registers ------------------------------------------
+    pdl_launch_dependents();
+    auto pair_row = [&](int pi) {                 // first of the two wqkv rows of pair pi
+        const int which = pi / (RP / 2), lp = pi - which * (RP / 2);
+        return which * D + head * HD + c * RP + 2 * lp;
+    };
+    uint4 pf0[PF], pf1[PF];
+    if (warp < NP) {
+        const uint4* w0 = reinterpret_cast<const uint4*>(W1 + (size_t)pair_row(warp) * D);
+        const uint4* w1 = reinterpret_cast<const uint4*>(W1 + (size_t)(pair_row(warp) + 1) * D);
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < D / EPC) { pf0[i] = ldg_stream(w0 + ch); pf1[i] = ldg_stream(w1 + ch); }
+        }
+    }
+    // out-projection slice: rows n0..n0+NR, columns head*HD..+HD; LPK lanes per row
+    const int NR = D / kCS, n0 = c * NR;
+    const int sub = lane % LPK, rsub = lane / LPK;
+    uint4 wo_pf[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int n = (warp + kFusedWarps * i) * KPI + rsub;
+        if (n < NR) wo_pf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
+    }
+    cluster.sync();                            // every block of the head is running: its shared memory may be written
+    pdl_wait();
+
+    // ---- residual, norm, this block's rows of q, k, v ----------------------------------------------------
+    const int pos = a.tok_pos[0], slot = a.tok_slot[0];
+    fused_prologue(a, xs, red, c == 0 && head == 0);
+    for (int pi = warp; pi < NP; pi += kFusedWarps) {
+        const int row = pair_row(pi);
+        float v0, v1;
+        pair_dot<WT, PF>(W1 + (size_t)row * D, W1 + (size_t)(row + 1) * D, pf0, pf1, pi == warp, xs, D, v0, v1);
+        const int which = pi / (RP / 2), d0 = c * RP + 2 * (pi - which * (RP / 2));
+        float o0 = v0, o1 = v1;
+        if (which < 2) {                       // interleaved-pair rotation, src/ops/rope.cpp:60-76
+            const float2 cs = a.rope[(size_t)pos * (HD / 2) + (d0 >> 1)];
+            o0 = v0 * cs.x - v1 * cs.y;
+            o1 = v0 * cs.y + v1 * cs.x;
+        }
+        float* dst_local = which == 0 ? s_q : (which == 1 ? s_k : s_v);
+        if (which > 0) {                       // the cache holds the rounded value; attention must see the same
+            const WT r0 = from_float<WT>(o0), r1 = from_float<WT>(o1);
+            o0 = to_float(r0); o1 = to_float(r1);
+            if (lane == 0) {
+                const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
+                WT* dst = kv_ptr<WT>(a.kv, a.m, a.layer, page, which - 1, head, pos % kPage) + d0;
+                dst[0] = r0; dst[1] = r1;
+            }
+        }
+        if (lane < kCS) {                      // lane r hands the pair to block r of the cluster
+            float* remote = cluster.map_shared_rank(dst_local, lane);
+            remote[d0] = o0; remote[d0 + 1] = o1;
+        }
+    }
+    cluster.sync();
+
+    // ---- attention over this block's pages (round-robin over the cluster) ---------------------------------
+    float qf[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) qf[e] = s_q[sub * EPC + e];
+    const int dp = tid % DP, kg = tid / DP;
+    float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
+    const int n_pages = pos / kPage + 1;
+    for (int pg = c; pg < n_pages; pg += kCS) {
+        const int kb = pg * kPage;
+        const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pg];
+        const WT* Kp = kv_ptr<WT>(a.kv, a.m, a.layer, page, 0, head, 0);
+        const WT* Vp = kv_ptr<WT>(a.kv, a.m, a.layer, page, 1, head, 0);
+        const int nk = min(kPage, pos + 1 - kb);
+        for (int j = warp * KPI + rsub; j < kPage; j += kFusedWarps * KPI) {
+            float s = 0.f;
+            if (j < nk) {
+                if (kb + j == pos) {           // the new key lives in shared memory (its cache row is being written)
+#pragma unroll
+                    for (int e = 0; e < EPC; ++e) s += qf[e] * s_k[sub * EPC + e];
+                } else {
+                    const uint4 v = *reinterpret_cast<const uint4*>(Kp + (size_t)j * HD + sub * EPC);
+                    float kf[EPC];
+                    unpack16<WT>(v, kf);
+#pragma unroll
+                    for (int e = 0; e < EPC; ++e) s += qf[e] * kf[e];
+                }
+            }
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (sub == 0) sc[j] = (j < nk) ? s * a.m.scale : -INFINITY;
+        }
+        __syncthreads();
+        float pm = -INFINITY;
+        for (int j = lane; j < kPage; j += 32) pm = fmaxf(pm, sc[j]);
+        pm = warp_max(pm);
+        const float m_new = fmaxf(m_run, pm);
+        const float corr = expf(m_run - m_new);
+        l_run *= corr; o0 *= corr; o1 *= corr;
+        m_run = m_new;
+        for (int j = kg; j < nk; j += KG) {
+            const float p = expf(sc[j] - m_new);
+            float v0, v1;
+            if (kb + j == pos) { v0 = s_v[2 * dp]; v1 = s_v[2 * dp + 1]; }
+            else if (sizeof(WT) == 2) {
+                const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(Vp + (size_t)j * HD + 2 * dp);
+                v0 = __low2float(vv); v1 = __high2float(vv);
+            } else {
+                const float2 vv = *reinterpret_cast<const float2*>(Vp + (size_t)j * HD + 2 * dp);
+                v0 = vv.x; v1 = vv.y;
+            }
+            l_run += p; o0 += p * v0; o1 += p * v1;
+        }
+        __syncthreads();
+    }
+    red_o[kg][2 * dp] = o0;
+    red_o[kg][2 * dp + 1] = o1;
+    if (dp == 0) red_l[kg] = l_run;
+    __syncthreads();
+    if (tid < HD + 2) {                        // hand (out, max, sum) to every block of the head
+        float val;
+        if (tid < HD) { val = 0.f; for (int g = 0; g < KG; ++g) val += red_o[g][tid]; }
+        else if (tid == HD) val = m_run;
+        else { val = 0.f; for (int g = 0; g < KG; ++g) val += red_l[g]; }
+        for (int r = 0; r < kCS; ++r) cluster.map_shared_rank(&s_part[0][0], r)[c * (HD + 2) + tid] = val;
+    }
+    cluster.sync();
+    if (tid < HD) {                            // merge in rank order
+        float mx = -INFINITY;
+        for (int r = 0; r < kCS; ++r) mx = fmaxf(mx, s_part[r][HD]);
+        float num = 0.f, den = 0.f;
+        for (int r = 0; r < kCS; ++r) {
+            const float mr = s_part[r][HD];
+            if (mr == -INFINITY) continue;
+            const float w = expf(mr - mx);
+            den += w * s_part[r][HD + 1];
+            num += w * s_part[r][tid];
+        }
+        s_att[tid] = num / den;
+    }
+    __syncthreads();
+
+    // ---- this head's share of the out-projection, rows n0..n0+NR -------------------------------------------
+    float af[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) af[e] = s_att[sub * EPC + e];
+    for (int i = 0, n = warp * KPI + rsub; n - rsub < NR; ++i, n += kFusedWarps * KPI) {
+        float s = 0.f;
+        if (n < NR) {
+            const uint4 v = i < 2 ? wo_pf[i < 1 ? 0 : 1]
+                                  : ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
+            float wf[EPC];
+            unpack16<WT>(v, wf);
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) s += af[e] * wf[e];
+        }
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (sub == 0 && n < NR) a.parts_out[(size_t)head * D + n0 + n] = s;
+    }
+}
+
+template <typename WT, int PF>
+__global__ void __launch_bounds__(kFusedThreads) k_ffn_block(const FusedArgs a) {
+    constexpr int EPC = Elems<WT>::per16;
+    constexpr int DPF = 3;                       // prefetched down-projection chunks per thread
+    extern __shared__ __align__(16) float smem[];
+    const int D = a.m.D, F = a.m.F;
+    float* xs = smem;                            // [D]
+    float* s_y = xs + D;                         // [G][D], then [D] in place of group 0
+    __shared__ float red[kFusedWarps];
+    __shared__ float s_hid[64];
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int c = (int)cluster.block_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const WT* W1 = reinterpret_cast<const WT*>(a.w1);
+    const WT* W2 = reinterpret_cast<const WT*>(a.w2);
+    const int upc = a.upc;
+    const int j0 = blockIdx.x * upc;
+    const int nu = max(0, min(upc, F - j0));     // hidden units of this block
+    const int NCH = D / EPC;                     // 16-byte chunks of a down-projection row
+    const int G = kFusedThreads / NCH;           // unit groups in the down phase (>= 1 by launch condition)
+    const int ch = tid % NCH, ug = tid / NCH;
+
+    pdl_launch_dependents();
+    uint4 pf0[PF], pf1[PF];
+    if (warp < nu) {
+        const uint4* w0 = reinterpret_cast<const uint4*>(W1 + (size_t)(2 * (j0 + warp)) * D);
+        const uint4* w1 = reinterpret_cast<const uint4*>(W1 + (size_t)(2 * (j0 + warp) + 1) * D);
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int cc = lane + 32 * i;
+            if (cc < NCH) { pf0[i] = ldg_stream(w0 + cc); pf1[i] = ldg_stream(w1 + cc); }
+        }
+    }
+    uint4 dpf[DPF];
+#pragma unroll
+    for (int i = 0; i < DPF; ++i) {
+        const int u = ug + G * i;
+        if (ug < G && u < nu) dpf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
+    }
+    pdl_wait();
+
+    fused_prologue(a, xs, red, blockIdx.x == 0);
+    // gate / up rows of this block's hidden units: silu(g) * u, src/nn/swiglu.cpp:37-57
+    for (int u = warp; u < nu; u += kFusedWarps) {
+        float g, up;
+        pair_dot<WT, PF>(W1 + (size_t)(2 * (j0 + u)) * D, W1 + (size_t)(2 * (j0 + u) + 1) * D, pf0, pf1, u == warp, xs, D, g, up);
+        if (lane == 0) {
+            const float sig = 1.0f / (1.0f + expf(-g));
+            s_hid[u] = (g * sig) * up;
+        }
+    }
+    __syncthreads();
+    // share of the down-projection: y[n] = sum_u hid[u] * Wd[j0+u][n]
+    if (ug < G) {
+        float acc[EPC];
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+        for (int i = 0, u = ug; u < nu; ++i, u += G) {
+            const uint4 v = i < DPF ? dpf[i < 1 ? 0 : (i < 2 ? 1 : 2)]
+                                    : ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
+            float wf[EPC];
+            unpack16<WT>(v, wf);
+            const float h = s_hid[u];
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) acc[e] += h * wf[e];
+        }
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) s_y[(size_t)ug * D + ch * EPC + e] = acc[e];
+    }
+    __syncthreads();
+    for (int n = tid; n < D; n += kFusedThreads) {
+        float s = s_y[n];
+        for (int g = 1; g < G; ++g) s += s_y[(size_t)g * D + n];
+        s_y[n] = s;
+    }
+    cluster.sync();
+    // block c of the cluster adds up columns [c*D/8, (c+1)*D/8) of the 8 blocks, in rank order
+    const int NR = D / kCS;
+    for (int n = tid; n < NR; n += kFusedThreads) {
+        float s = 0.f;
+        for (int r = 0; r < kCS; ++r) s += cluster.map_shared_rank(s_y, r)[c * NR + n];
+        a.parts_out[(size_t)(blockIdx.x / kCS) * D + c * NR + n] = s;
+    }
+    cluster.sync();                              // peers may still be reading this block's shared memory
+}
+
+}  // namespace sllm

@@ -23,6 +23,7 @@
 #include "../../include/sllm.h"
 #include "attn_decode.cuh"
 #include "common.cuh"
+#include "decode_fused.cuh"
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "repack.cuh"
@@ -105,9 +106,15 @@ struct sllm_engine {
     CUtensorMap map_head{};
     std::map<std::pair<const void*, int>, CUtensorMap> map_x;    // (activation buffer, BN) -> map
     int tc_min_tokens = 17;
+    // fused single-token decode path
+    float* xb = nullptr; float* attn_parts = nullptr; float* down_parts = nullptr;
+    std::vector<void*> wdT;                          // per layer: down weights as [F][D]
+    int fused_upc = 0, fused_nb = 0;
+    bool fused_ok = false;
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
+    unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
     // draws
     double* d_draws = nullptr; size_t draws_cap = 0;
     // host pinned
@@ -398,9 +405,75 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
     return SLLM_OK;
 }
 
+
+// ---- fused single-token decode path (decode_fused.cuh) ------------------------------------------------------
+template <typename... KArgs>
+int launch_cluster(sllm_engine* e, void (*kern)(KArgs...), dim3 grid, size_t smem, bool pdl, const FusedArgs& a) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kFusedThreads); cfg.dynamicSmemBytes = smem; cfg.stream = e->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+    CU(cudaLaunchKernelEx(&cfg, kern, a));
+    e->launches += 1;
+    return SLLM_OK;
+}
+
+template <typename WT, int PF>
+int launch_attn_block(sllm_engine* e, const FusedArgs& a, bool pdl) {
+    const dim3 grid(kCS, a.m.H);
+    const size_t smem = (size_t)a.m.D * sizeof(float);
+    switch (a.m.hd) {
+        case 16: return launch_cluster(e, k_attn_block<WT, 16, PF>, grid, smem, pdl, a);
+        case 32: return launch_cluster(e, k_attn_block<WT, 32, PF>, grid, smem, pdl, a);
+        case 64: return launch_cluster(e, k_attn_block<WT, 64, PF>, grid, smem, pdl, a);
+        case 128: return launch_cluster(e, k_attn_block<WT, 128, PF>, grid, smem, pdl, a);
+    }
+    return fail(e, SLLM_ERR_INVALID, "unsupported head_dim");
+}
+
+template <typename WT>
+int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logits, bool pdl) {
+    const ModelDims& m = e->md;
+    const int chunks_per_lane = (m.D / Elems<WT>::per16 + 31) / 32;
+    const int G = kFusedThreads / (m.D / Elems<WT>::per16);
+    const size_t smem_b = (size_t)(1 + G) * m.D * sizeof(float);
+    const int ncl = e->fused_nb / kCS;
+    FusedArgs a{};
+    a.m = m; a.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    a.tok_id = pv.tok_id; a.tok_slot = pv.tok_slot; a.tok_pos = pv.tok_pos; a.rope = e->rope; a.upc = e->fused_upc;
+    for (int l = 0; l < m.L; ++l) {
+        const LayerW& w = e->layers[l];
+        a.layer = l;
+        // attention block: reads xb + down partials of the previous layer (layer 0: the embedding row), writes x
+        a.x_in = e->xb; a.parts_in = e->down_parts; a.n_parts_in = l == 0 ? 0 : ncl; a.x_out = e->x;
+        a.emb = l == 0 ? e->emb_f32 : nullptr; a.gain = w.g_attn; a.w1 = w.wqkv; a.w2 = w.wo; a.parts_out = e->attn_parts;
+        int rc = chunks_per_lane > 3 ? launch_attn_block<WT, 7>(e, a, pdl) : launch_attn_block<WT, 3>(e, a, pdl);
+        if (rc) return rc;
+        // FFN block: reads x + attention partials, writes xb
+        a.x_in = e->x; a.parts_in = e->attn_parts; a.n_parts_in = m.H; a.x_out = e->xb; a.emb = nullptr;
+        a.gain = w.g_ffn; a.w1 = w.wgu; a.w2 = e->wdT[l]; a.parts_out = e->down_parts;
+        rc = chunks_per_lane > 3 ? launch_cluster(e, k_ffn_block<WT, 7>, dim3(e->fused_nb), smem_b, pdl, a)
+                                 : launch_cluster(e, k_ffn_block<WT, 3>, dim3(e->fused_nb), smem_b, pdl, a);
+        if (rc) return rc;
+    }
+    if (n_rows > 0) {
+        GemvArgs h{};
+        h.m = m; h.eps = m.eps; h.W = e->emb_w; h.R = m.V; h.K = m.D; h.in = e->xb; h.gain = e->g_final;
+        h.parts = e->down_parts; h.n_parts = ncl; h.out = logits; h.n_tok = 1; h.pass = pv;
+        return launch_gemv<WT, kModeHead>(e, h, pdl);
+    }
+    return SLLM_OK;
+}
+
 int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl) { return launch_attn<__nv_bfloat16>(e, t, pdl); }
 
 int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    if (pv.n_tok == 1 && e->fused_ok && (n_rows == 0 || row_tok == nullptr))
+        return e->f32 ? run_pass_fused_t<float>(e, pv, n_rows, logits, pdl) : run_pass_fused_t<__nv_bfloat16>(e, pv, n_rows, logits, pdl);
     if (!e->f32 && e->encode_tiled && pv.n_tok >= e->tc_min_tokens) return run_pass_tc(e, pv, row_tok, n_rows, logits, pdl);
     return e->f32 ? run_pass_t<float>(e, pv, row_tok, n_rows, logits, pdl)
                   : run_pass_t<__nv_bfloat16>(e, pv, row_tok, n_rows, logits, pdl);
@@ -469,6 +542,7 @@ SampleArgs make_sample_args(sllm_engine* e, const sllm_sampling* o, int n_slots,
     s.temperature = o->temperature; s.top_p = o->top_p; s.penalty = o->repetition_penalty;
     s.eos = o->eos_token; s.stop_token = o->stop_token;
     s.draws = d_draws; s.n_slots = n_slots; s.draws_stride = stride; s.seeded = seeded;
+    s.g_mass = e->samp_mass; s.g_cnt = e->samp_cnt;
     s.next_tok_id = e->d_dec_id; s.next_tok_pos = e->d_dec_pos; s.next_tok_slot = e->d_dec_slot;
     return s;
 }
@@ -616,7 +690,13 @@ int convert_param(sllm_engine* e, const ParamSlot& p) {
         case 5: return transpose((void*)lw->wo, m.D, m.D, 1, 0, 0);
         case 7: return transpose((void*)lw->wgu, m.D, m.F, 2, 0, 0);
         case 8: return transpose((void*)lw->wgu, m.D, m.F, 2, 1, 0);
-        case 9: return transpose((void*)lw->wd, m.F, m.D, 1, 0, 0);
+        case 9: {
+            int rc = transpose((void*)lw->wd, m.F, m.D, 1, 0, 0);
+            if (rc || !e->fused_ok) return rc;
+            // the fused decode kernels read the down weights row-per-hidden-unit: the reference's own [F][D]
+            return launch(e, k_cast<WT>, dim3(e->sm_count * 4), dim3(256), 0, false, (const float*)e->staging,
+                          static_cast<WT*>(e->wdT[p.layer]), n);
+        }
     }
     return fail(e, SLLM_ERR_INVALID, "unknown parameter kind");
 }
@@ -910,6 +990,23 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->att, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->hid, (size_t)e->pass_cap * F, &e->scratch_bytes);
     A(&e->step_logits, (size_t)e->max_batch * V, &e->scratch_bytes);
     A(&e->pass_logits, (size_t)e->logit_rows_cap * V, &e->scratch_bytes);
+    {   // fused single-token path: shapes it supports
+        const int epc = e->f32 ? 4 : 8;
+        const int nch = (int)D / epc;
+        e->fused_upc = std::max<int>((int)((F + 143) / 144), 2);
+        e->fused_nb = (int)(((F + e->fused_upc - 1) / e->fused_upc + kCS - 1) / kCS) * kCS;
+        e->fused_ok = nch <= kFusedThreads && e->fused_upc <= 64 && D % kCS == 0 &&
+                      (size_t)(1 + kFusedThreads / nch) * D * sizeof(float) <= 48 * 1024;
+        if (e->fused_ok) {
+            A(&e->xb, D, &e->scratch_bytes);
+            A(&e->attn_parts, H * D, &e->scratch_bytes);
+            A(&e->down_parts, (size_t)(e->fused_nb / kCS) * D, &e->scratch_bytes);
+            e->wdT.resize(L);
+            for (uint64_t l = 0; l < L; ++l) { unsigned char* p = nullptr; A(&p, D * F * ws, &e->weight_bytes); e->wdT[l] = p; }
+        }
+    }
+    A(&e->samp_mass, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
+    A(&e->samp_cnt, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
     A(&e->d_status, 4, &e->scratch_bytes);
     if (!e->f32) {
         A(&e->xn16, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->att16, (size_t)e->pass_cap * D, &e->scratch_bytes);

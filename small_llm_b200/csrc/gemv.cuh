@@ -35,6 +35,8 @@ struct GemvArgs {
     PassView pass;
     int layer;
     const float2* rope;       // [ctx][hd/2] (cos, sin)
+    const float* parts;       // single-token passes: [n_parts][K] partial sums that complete the residual `in`
+    int n_parts;
     const float* emb;         // layer 0: fp32 embedding table [V][D]; x is gathered from it ...
     float* x_out;             // ... and written here by block column 0
     float eps;
@@ -89,7 +91,11 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
             if (MODE == kModeQKV && a.emb) src = a.emb + (size_t)a.pass.tok_id[ptok] * K;
             else src = a.in + (size_t)ptok * K;
             for (int k = tid * 4; k < K; k += kGemvThreads * 4) {
-                const float4 v = *reinterpret_cast<const float4*>(src + k);
+                float4 v = *reinterpret_cast<const float4*>(src + k);
+                for (int p = 0; p < a.n_parts; ++p) {          // fixed order: the sum is reproducible
+                    const float4 q = __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)p * K + k));
+                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                }
                 *reinterpret_cast<float4*>(xs + t * K + k) = v;
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
                 if (MODE == kModeQKV && a.emb && blockIdx.x == 0)

@@ -43,6 +43,11 @@ struct SampleArgs {
     int draws_stride;
     int seeded;                   // 0: one entry per sampling step.  1: an entry is consumed only when at least
                                   //    two candidates are kept (std::discrete_distribution's behaviour)
+    // level-0 histogram in global memory: [n_slots][1024] mass and counts.  One block cannot push 32768 x 4
+    // atomics through its shared-memory atomic unit quickly (about one lane per clock); fire-and-forget
+    // reductions in L2 are spread over many memory slices.
+    unsigned long long* g_mass;
+    unsigned int* g_cnt;
     // next-pass token list, written for the decode step that follows
     uint32_t* next_tok_id;
     int* next_tok_pos;
@@ -94,13 +99,17 @@ struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned i
 // Scans histogram h (keys lo..hi, bucket = (key-lo)>>sh) from the highest bucket down and picks the first
 // non-empty bucket at which cum + running mass reaches target.  Returns false when none does; then cum / cnt
 // have absorbed the whole range.  On success lo/hi shrink to the picked bucket and cum / cnt count what lies above.
-__device__ bool scan_pick(const SampHist& h, SampScratch& s, unsigned long long target, uint32_t& lo, uint32_t& hi, int sh,
+__device__ bool scan_pick(const SampHist& h, const unsigned long long* gm, const unsigned int* gc, SampScratch& s,
+                          unsigned long long target, uint32_t& lo, uint32_t& hi, int sh,
                           unsigned long long& cum, unsigned int& cnt, unsigned long long& bucket_mass, unsigned int& bucket_cnt) {
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int top = (int)((hi - lo) >> sh);
     const int b = top - tid;
     unsigned long long my_m = 0; unsigned int my_c = 0;
-    if (b >= 0) { my_m = hist_mass(h, b); my_c = h.cnt[b]; }
+    if (b >= 0) {
+        if (gm) { my_m = __ldcg(gm + b); my_c = __ldcg(gc + b); }
+        else { my_m = hist_mass(h, b); my_c = h.cnt[b]; }
+    }
     unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -138,7 +147,7 @@ __device__ bool scan_pick(const SampHist& h, SampScratch& s, unsigned long long 
 // Finds the element, in descending (key, then ascending id) order, at which the running mass first reaches
 // `target`.  h0 is the histogram of the whole range [kmin, kmax] with shift sh0; h1 is working space.
 __device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t kmin, uint32_t kmax, int sh0,
-                                    const SampHist& h0, SampHist& h1, SampScratch& s) {
+                                    const unsigned long long* gm, const unsigned int* gc, SampHist& h1, SampScratch& s) {
     const int tid = threadIdx.x;
     uint32_t lo = kmin, hi = kmax;
     unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
@@ -146,7 +155,6 @@ __device__ SelectResult select_mass(const float* w, int V, unsigned long long ta
     res.found = 0; res.qk = 0; res.ties = 0; res.r = 0;
     int sh = sh0;
     for (int pass = 0; pass < 5; ++pass) {
-        const SampHist* h = &h0;
         if (pass > 0) {
             sh = shift_for(hi - lo);
             hist_clear(h1);
@@ -156,9 +164,8 @@ __device__ SelectResult select_mass(const float* w, int V, unsigned long long ta
                 if (key >= lo && key <= hi) hist_add(h1, (int)((key - lo) >> sh), fix_of(w[i]));
             }
             __syncthreads();
-            h = &h1;
         }
-        if (!scan_pick(*h, s, target, lo, hi, sh, cum, cnt, bm, bc)) break;
+        if (!scan_pick(h1, pass == 0 ? gm : nullptr, gc, s, target, lo, hi, sh, cum, cnt, bm, bc)) break;
         if (sh == 0) {                       // one key per bucket: done
             res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
             const unsigned long long need = target > cum ? target - cum : 0;
@@ -207,7 +214,7 @@ __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r,
 
 __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
     extern __shared__ __align__(16) float w[];                 // [V] scores, then weights
-    __shared__ SampHist h0, h1;
+    __shared__ SampHist h1;
     __shared__ SampScratch sc;
     __shared__ float r_val[32];
     __shared__ int r_idx[32];
@@ -227,6 +234,9 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
     int n_tok = a.st.n_tok[slot];
     const int fin = a.st.finished[slot];
     int token = -1;
+    unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
+    unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
+    for (int b = tid; b < kSampBuckets; b += kSampThreads) { gm[b] = 0ull; gc[b] = 0u; }
 
     if (!fin) {
         const float* lg = a.logits + (size_t)slot * V;
@@ -278,7 +288,6 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
                 kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
             }
             if (lane == 0) { r_sum[wp] = sum; r_kmin[wp] = kmin; }
-            hist_clear(h0);
             __syncthreads();
             if (tid == 0) {
                 unsigned long long t = 0; uint32_t k = 0xffffffffu;
@@ -293,13 +302,16 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
             const int sh0 = shift_for(kmax - klo);
             for (int i = tid; i < V; i += kSampThreads) {
                 const float e = w[i];
-                hist_add(h0, (int)((__float_as_uint(e) - klo) >> sh0), fix_of(e));
+                const int b = (int)((__float_as_uint(e) - klo) >> sh0);
+                atomicAdd(gm + b, fix_of(e));                  // results are not used: compiled to reductions
+                atomicAdd(gc + b, 1u);
             }
+            __threadfence();
             __syncthreads();
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
-            const SelectResult cut = select_mass(w, V, t1, klo, kmax, sh0, h0, h1, sc);
+            const SelectResult cut = select_mass(w, V, t1, klo, kmax, sh0, gm, gc, h1, sc);
             unsigned long long kept_mass; unsigned int kept;
             if (cut.found) { kept_mass = cut.cum_above + (unsigned long long)cut.r * cut.qk; kept = cut.cnt_above + cut.r; }
             else { kept_mass = cut.cum_above; kept = cut.cnt_above; }
@@ -308,7 +320,7 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
             if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
-            const SelectResult hit = select_mass(w, V, t2, klo, kmax, sh0, h0, h1, sc);
+            const SelectResult hit = select_mass(w, V, t2, klo, kmax, sh0, gm, gc, h1, sc);
             uint32_t key; unsigned int r;
             if (hit.found && (hit.cnt_above + hit.r) <= kept) { key = hit.key; r = hit.r; }
             else if (cut.found) { key = cut.key; r = cut.r; }                  // last kept candidate
