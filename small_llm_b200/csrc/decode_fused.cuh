@@ -109,7 +109,7 @@ __device__ __forceinline__ void pair_dot(const WT* w0p, const WT* w1p, const uin
 }
 
 template <typename WT, int HD, int PF>
-__global__ void __launch_bounds__(kFusedThreads) k_attn_block(const FusedArgs a) {
+__global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs a) {
     constexpr int EPC = Elems<WT>::per16;
     constexpr int RP = HD / kCS;                 // rows of q (and of k, of v) per block
     constexpr int NP = 3 * RP / 2;               // row pairs per block
@@ -281,11 +281,9 @@ __global__ void __launch_bounds__(kFusedThreads) k_attn_block(const FusedArgs a)
     float af[EPC];
 #pragma unroll
     for (int e = 0; e < EPC; ++e) af[e] = s_att[sub * EPC + e];
-    for (int i = 0, n = warp * KPI + rsub; n - rsub < NR; ++i, n += kFusedWarps * KPI) {
+    auto out_row = [&](const uint4& v, int n) {
         float s = 0.f;
         if (n < NR) {
-            const uint4 v = i < 2 ? wo_pf[i < 1 ? 0 : 1]
-                                  : ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
             float wf[EPC];
             unpack16<WT>(v, wf);
 #pragma unroll
@@ -294,11 +292,21 @@ __global__ void __launch_bounds__(kFusedThreads) k_attn_block(const FusedArgs a)
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (sub == 0 && n < NR) a.parts_out[(size_t)head * D + n0 + n] = s;
+    };
+    const int nbase = warp * KPI;                       // warp-uniform loop bounds: the shuffles need whole warps
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+        if (nbase + kFusedWarps * KPI * i < NR) out_row(wo_pf[i], nbase + kFusedWarps * KPI * i + rsub);
+    for (int nb = nbase + 2 * kFusedWarps * KPI; nb < NR; nb += kFusedWarps * KPI) {
+        const int n = nb + rsub;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n < NR) v = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
+        out_row(v, n);
     }
 }
 
 template <typename WT, int PF>
-__global__ void __launch_bounds__(kFusedThreads) k_ffn_block(const FusedArgs a) {
+__global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs a) {
     constexpr int EPC = Elems<WT>::per16;
     constexpr int DPF = 3;                       // prefetched down-projection chunks per thread
     extern __shared__ __align__(16) float smem[];
@@ -355,15 +363,18 @@ __global__ void __launch_bounds__(kFusedThreads) k_ffn_block(const FusedArgs a) 
         float acc[EPC];
 #pragma unroll
         for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
-        for (int i = 0, u = ug; u < nu; ++i, u += G) {
-            const uint4 v = i < DPF ? dpf[i < 1 ? 0 : (i < 2 ? 1 : 2)]
-                                    : ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
+        auto down_row = [&](const uint4& v, int u) {
             float wf[EPC];
             unpack16<WT>(v, wf);
             const float h = s_hid[u];
 #pragma unroll
             for (int e = 0; e < EPC; ++e) acc[e] += h * wf[e];
-        }
+        };
+#pragma unroll
+        for (int i = 0; i < DPF; ++i)
+            if (ug + G * i < nu) down_row(dpf[i], ug + G * i);
+        for (int u = ug + G * DPF; u < nu; u += G)
+            down_row(ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch), u);
 #pragma unroll
         for (int e = 0; e < EPC; ++e) s_y[(size_t)ug * D + ch * EPC + e] = acc[e];
     }
@@ -382,6 +393,18 @@ __global__ void __launch_bounds__(kFusedThreads) k_ffn_block(const FusedArgs a) 
         a.parts_out[(size_t)(blockIdx.x / kCS) * D + c * NR + n] = s;
     }
     cluster.sync();                              // peers may still be reading this block's shared memory
+}
+
+// x[k] = base[k] + sum of partials, for callers that want the finished residual stream in one buffer
+__global__ void __launch_bounds__(256) k_sum_parts(const float* __restrict__ base, const float* __restrict__ parts, int n_parts,
+                                                   int D, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < D; k += gridDim.x * blockDim.x) {
+        float v = base[k];
+        for (int p = 0; p < n_parts; ++p) v += __ldcg(parts + (size_t)p * D + k);
+        out[k] = v;
+    }
 }
 
 }  // namespace sllm

@@ -466,7 +466,9 @@ int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logi
         h.parts = e->down_parts; h.n_parts = ncl; h.out = logits; h.n_tok = 1; h.pass = pv;
         return launch_gemv<WT, kModeHead>(e, h, pdl);
     }
-    return SLLM_OK;
+    // no logits wanted: leave the finished residual in e->x, where the other paths keep it
+    return launch(e, k_sum_parts, dim3((m.D + 255) / 256), dim3(256), 0, pdl, (const float*)e->xb, (const float*)e->down_parts,
+                  ncl, m.D, e->x);
 }
 
 int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl) { return launch_attn<__nv_bfloat16>(e, t, pdl); }
