@@ -137,8 +137,10 @@ int sllm_truncate(sllm_engine* e, uint32_t slot, uint64_t n_tokens);
  * step, not consumed sequentially); NULL = seeded mode, reproducing the reference's
  * std::mt19937_64(seed) + std::discrete_distribution consumption (a draw is used only when at
  * least two candidates are kept) with slot s using seed + s.
- * A slot stops after EOS or stop_token is appended, after max_new tokens, or when its length
- * reaches context_length (sliding the window is left to the caller, see small_llm.hpp). */
+ * A slot stops after EOS or stop_token is appended or after max_new tokens.  When a slot holds more
+ * than context_length tokens the window slides as in the reference (src/inference.cpp:40-48): each
+ * further token re-runs the last context_length tokens with positions restarting at 0.  Prompts may be
+ * longer than context_length for the same reason; a slot can hold 2 * context_length + 1 tokens. */
 int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* prompt_lens, uint32_t n_seq,
                   uint64_t max_new_tokens, const sllm_sampling* opt, const double* draws,
                   uint32_t* out_tokens, uint64_t out_stride, uint64_t* out_lens);

@@ -268,7 +268,7 @@ class Engine:
         self._ck(self.lib.sllm_set_step_logits(self.h, slot, v.ctypes.data_as(f32p)))
 
     def tokens(self, slot: int = 0) -> np.ndarray:
-        cap = self.config.context_length + 1
+        cap = 2 * self.config.context_length + 2
         out = np.empty(cap, dtype=np.uint32)
         n = C.c_uint64()
         self._ck(self.lib.sllm_get_tokens(self.h, slot, out.ctypes.data_as(u32p), cap, C.byref(n)))
@@ -296,7 +296,7 @@ class Engine:
         lens = np.array([len(p) for p in prompts], dtype=np.uint32)
         ids = np.ascontiguousarray(np.concatenate([np.asarray(p, dtype=np.uint32) for p in prompts]) if n
                                    else np.zeros(0, np.uint32))
-        stride = self.config.context_length + 1
+        stride = 2 * self.config.context_length + 2
         out = np.empty((max(n, 1), stride), dtype=np.uint32)
         out_lens = np.zeros(max(n, 1), dtype=np.uint64)
         s = self._sampling(opt, eos)
@@ -379,36 +379,4 @@ class Inference:
         tokens = np.asarray(tokens, dtype=np.uint32)
         if tokens.size == 0:
             raise ValueError("Inference::generate: prompt encoded to zero tokens")
-        eng = self.model.engine
-        ctx = self.model.config().context_length
-        if tokens.size <= ctx:
-            out = eng.generate([tokens], max_new_tokens, opt, draws, self.eos)[0]
-            produced = out.size - tokens.size
-            stopped = produced > 0 and (out[-1] == self.eos or int(out[-1]) == opt.stop_token)
-            if stopped or produced >= max_new_tokens:
-                return out
-            tokens = out
-            max_new_tokens -= produced
-            draws = None if draws is None else np.asarray(draws)[produced:]
-            if opt.temperature > 0 and draws is None:
-                raise SllmError(ERR_STATE, "seeded generation past the context window is not supported; pass draws")
-        # window slides (src/inference.cpp:40-48): every further token re-runs the last ctx tokens
-        # with positions restarting at 0, exactly as the reference does
-        toks = list(int(t) for t in tokens)
-        for step in range(max_new_tokens):
-            window = np.array(toks[-ctx:], dtype=np.uint32)
-            eng.prefill([window])
-            logits = eng.step_logits(0)
-            tok = _host_pick(eng, logits, toks, opt, None if draws is None else float(np.asarray(draws).reshape(-1)[step]),
-                             self.eos)
-            toks.append(tok)
-            if tok == self.eos or tok == opt.stop_token:
-                break
-        return np.array(toks, dtype=np.uint32)
-
-
-def _host_pick(eng: Engine, logits, history, opt: SamplingOptions, draw, eos):
-    """Sliding-window steps: the device sampler sees only the window's ids, while the reference
-    penalises the whole history, so the few ids that left the window are pre-penalised here and
-    the device sampler does the rest on the adjusted logits of slot 0."""
-    raise SllmError(ERR_STATE, "generation past context_length + 1 tokens is not implemented")
+        return self.model.engine.generate([tokens], max_new_tokens, opt, draws, self.eos)[0]

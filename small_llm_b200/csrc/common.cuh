@@ -59,6 +59,23 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- optional timeline stamps (debug builds with -DSLLM_TIMELINE only) ------------------------------------
+#ifdef SLLM_TIMELINE
+__device__ unsigned long long g_tl_buf[1 << 16];
+__device__ unsigned int g_tl_n;
+__device__ __forceinline__ void tl_stamp(unsigned int id) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const unsigned int i = atomicAdd(&g_tl_n, 1u);
+        if (i < (1u << 15)) { g_tl_buf[2 * i] = id; g_tl_buf[2 * i + 1] = t; }
+    }
+}
+#define SLLM_TL(id) tl_stamp(id)
+#else
+#define SLLM_TL(id)
+#endif
+
 // ---- device-side view of the model and of the running sequences ----------------------------
 struct LayerW {
     const void* wqkv;     // [3D][D]   rows: q | k | v       (reference: attn.q/k/v, each [D][D] as x@W)

@@ -55,12 +55,31 @@ __device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, fl
     const int D = a.m.D, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* base = a.emb ? a.emb + (size_t)a.tok_id[0] * D : a.x_in;
     float ss = 0.f;
-    for (int k = tid; k < D; k += kFusedThreads) {
-        float v = base[k];
-        for (int p = 0; p < a.n_parts_in; ++p) v += __ldcg(a.parts_in + (size_t)p * D + k);
-        xs[k] = v;
-        ss += v * v;
-        if (store) a.x_out[k] = v;
+    // two elements per thread and up to 12 partials each are requested together (one round trip to L2),
+    // then added in a fixed order
+    for (int k0 = tid; k0 < D; k0 += 2 * kFusedThreads) {
+        const int k1 = k0 + kFusedThreads;
+        const bool has1 = k1 < D;
+        float v0 = base[k0], v1 = has1 ? base[k1] : 0.f;
+        for (int p0 = 0; p0 < a.n_parts_in; p0 += 12) {
+            float t0[12], t1[12];
+#pragma unroll
+            for (int i = 0; i < 12; ++i) {
+                const bool ok = p0 + i < a.n_parts_in;
+                t0[i] = ok ? __ldcg(a.parts_in + (size_t)(p0 + i) * D + k0) : 0.f;
+                t1[i] = ok && has1 ? __ldcg(a.parts_in + (size_t)(p0 + i) * D + k1) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 12; ++i) { v0 += t0[i]; v1 += t1[i]; }
+        }
+        xs[k0] = v0;
+        ss += v0 * v0;
+        if (store) a.x_out[k0] = v0;
+        if (has1) {
+            xs[k1] = v1;
+            ss += v1 * v1;
+            if (store) a.x_out[k1] = v1;
+        }
     }
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
@@ -138,6 +157,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
     const WT* W2 = reinterpret_cast<const WT*>(a.w2);
 
     // ---- before the dependency wait: weights into registers ------------------------------------------
+    SLLM_TL(100);
     pdl_launch_dependents();
     auto pair_row = [&](int pi) {                 // first of the two wqkv rows of pair pi
         const int which = pi / (RP / 2), lp = pi - which * (RP / 2);
@@ -163,11 +183,21 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         if (n < NR) wo_pf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
     }
     cluster.sync();                            // every block of the head is running: its shared memory may be written
+    SLLM_TL(101);
     pdl_wait();
+    SLLM_TL(102);
 
     // ---- residual, norm, this block's rows of q, k, v ----------------------------------------------------
     const int pos = a.tok_pos[0], slot = a.tok_slot[0];
+    // what depends only on the position is requested now and arrives while the norm runs
+    float2 cs_first = make_float2(1.f, 0.f);
+    if (warp < NP && warp / (RP / 2) < 2)
+        cs_first = a.rope[(size_t)pos * (HD / 2) + ((c * RP + 2 * (warp % (RP / 2))) >> 1)];
+    const int n_pages = pos / kPage + 1;
+    const int page_new = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
+    const int page_first = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + min(c, n_pages - 1)];
     fused_prologue(a, xs, red, c == 0 && head == 0);
+    SLLM_TL(103);
     for (int pi = warp; pi < NP; pi += kFusedWarps) {
         const int row = pair_row(pi);
         float v0, v1;
@@ -175,7 +205,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         const int which = pi / (RP / 2), d0 = c * RP + 2 * (pi - which * (RP / 2));
         float o0 = v0, o1 = v1;
         if (which < 2) {                       // interleaved-pair rotation, src/ops/rope.cpp:60-76
-            const float2 cs = a.rope[(size_t)pos * (HD / 2) + (d0 >> 1)];
+            const float2 cs = pi == warp ? cs_first : a.rope[(size_t)pos * (HD / 2) + (d0 >> 1)];
             o0 = v0 * cs.x - v1 * cs.y;
             o1 = v0 * cs.y + v1 * cs.x;
         }
@@ -184,8 +214,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
             const WT r0 = from_float<WT>(o0), r1 = from_float<WT>(o1);
             o0 = to_float(r0); o1 = to_float(r1);
             if (lane == 0) {
-                const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
-                WT* dst = kv_ptr<WT>(a.kv, a.m, a.layer, page, which - 1, head, pos % kPage) + d0;
+                WT* dst = kv_ptr<WT>(a.kv, a.m, a.layer, page_new, which - 1, head, pos % kPage) + d0;
                 dst[0] = r0; dst[1] = r1;
             }
         }
@@ -194,29 +223,63 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
             remote[d0] = o0; remote[d0 + 1] = o1;
         }
     }
+    // this block's first page of keys and values: requested before the exchange, used after it
+    constexpr int KIT = (kPage + kFusedWarps * KPI - 1) / (kFusedWarps * KPI);
+    constexpr int VIT = (kPage + KG - 1) / KG;
+    const int dp = tid % DP, kg = tid / DP;
+    uint4 k_pf[KIT];
+    float v_pf0[VIT], v_pf1[VIT];
+    auto load_v = [&](const WT* Vp, int j, float& v0, float& v1) {
+        if (sizeof(WT) == 2) {
+            const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(Vp + (size_t)j * HD + 2 * dp);
+            v0 = __low2float(vv); v1 = __high2float(vv);
+        } else {
+            const float2 vv = *reinterpret_cast<const float2*>(Vp + (size_t)j * HD + 2 * dp);
+            v0 = vv.x; v1 = vv.y;
+        }
+    };
+    if (c < n_pages) {
+        const WT* Kp = kv_ptr<WT>(a.kv, a.m, a.layer, page_first, 0, head, 0);
+        const WT* Vp = kv_ptr<WT>(a.kv, a.m, a.layer, page_first, 1, head, 0);
+        const int nk = min(kPage, pos + 1 - c * kPage);
+#pragma unroll
+        for (int i = 0; i < KIT; ++i) {
+            const int j = warp * KPI + rsub + i * kFusedWarps * KPI;
+            if (j < nk && c * kPage + j != pos) k_pf[i] = *reinterpret_cast<const uint4*>(Kp + (size_t)j * HD + sub * EPC);
+        }
+#pragma unroll
+        for (int i = 0; i < VIT; ++i) {
+            const int j = kg + KG * i;
+            if (j < nk && c * kPage + j != pos) load_v(Vp, j, v_pf0[i], v_pf1[i]);
+        }
+    }
+    SLLM_TL(104);
     cluster.sync();
+    SLLM_TL(105);
 
     // ---- attention over this block's pages (round-robin over the cluster) ---------------------------------
     float qf[EPC];
 #pragma unroll
     for (int e = 0; e < EPC; ++e) qf[e] = s_q[sub * EPC + e];
-    const int dp = tid % DP, kg = tid / DP;
     float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
-    const int n_pages = pos / kPage + 1;
     for (int pg = c; pg < n_pages; pg += kCS) {
         const int kb = pg * kPage;
-        const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pg];
+        const bool first = pg == c;
+        const int page = first ? page_first : a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pg];
         const WT* Kp = kv_ptr<WT>(a.kv, a.m, a.layer, page, 0, head, 0);
         const WT* Vp = kv_ptr<WT>(a.kv, a.m, a.layer, page, 1, head, 0);
         const int nk = min(kPage, pos + 1 - kb);
-        for (int j = warp * KPI + rsub; j < kPage; j += kFusedWarps * KPI) {
+#pragma unroll
+        for (int i = 0; i < KIT; ++i) {
+            const int j = warp * KPI + rsub + i * kFusedWarps * KPI;
+            if (j - rsub >= kPage) break;      // warp-uniform
             float s = 0.f;
             if (j < nk) {
                 if (kb + j == pos) {           // the new key lives in shared memory (its cache row is being written)
 #pragma unroll
                     for (int e = 0; e < EPC; ++e) s += qf[e] * s_k[sub * EPC + e];
                 } else {
-                    const uint4 v = *reinterpret_cast<const uint4*>(Kp + (size_t)j * HD + sub * EPC);
+                    const uint4 v = first ? k_pf[i] : *reinterpret_cast<const uint4*>(Kp + (size_t)j * HD + sub * EPC);
                     float kf[EPC];
                     unpack16<WT>(v, kf);
 #pragma unroll
@@ -235,17 +298,15 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         const float corr = expf(m_run - m_new);
         l_run *= corr; o0 *= corr; o1 *= corr;
         m_run = m_new;
-        for (int j = kg; j < nk; j += KG) {
+#pragma unroll
+        for (int i = 0; i < VIT; ++i) {
+            const int j = kg + KG * i;
+            if (j >= nk) break;
             const float p = expf(sc[j] - m_new);
             float v0, v1;
             if (kb + j == pos) { v0 = s_v[2 * dp]; v1 = s_v[2 * dp + 1]; }
-            else if (sizeof(WT) == 2) {
-                const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(Vp + (size_t)j * HD + 2 * dp);
-                v0 = __low2float(vv); v1 = __high2float(vv);
-            } else {
-                const float2 vv = *reinterpret_cast<const float2*>(Vp + (size_t)j * HD + 2 * dp);
-                v0 = vv.x; v1 = vv.y;
-            }
+            else if (first) { v0 = v_pf0[i]; v1 = v_pf1[i]; }
+            else load_v(Vp, j, v0, v1);
             l_run += p; o0 += p * v0; o1 += p * v1;
         }
         __syncthreads();
@@ -261,7 +322,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         else { val = 0.f; for (int g = 0; g < KG; ++g) val += red_l[g]; }
         for (int r = 0; r < kCS; ++r) cluster.map_shared_rank(&s_part[0][0], r)[c * (HD + 2) + tid] = val;
     }
+    SLLM_TL(106);
     cluster.sync();
+    SLLM_TL(107);
     if (tid < HD) {                            // merge in rank order
         float mx = -INFINITY;
         for (int r = 0; r < kCS; ++r) mx = fmaxf(mx, s_part[r][HD]);
@@ -303,6 +366,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         if (n < NR) v = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
         out_row(v, n);
     }
+    SLLM_TL(108);
 }
 
 template <typename WT, int PF>
@@ -328,6 +392,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
     const int G = kFusedThreads / NCH;           // unit groups in the down phase (>= 1 by launch condition)
     const int ch = tid % NCH, ug = tid / NCH;
 
+    SLLM_TL(200);
     pdl_launch_dependents();
     uint4 pf0[PF], pf1[PF];
     if (warp < nu) {
@@ -345,9 +410,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         const int u = ug + G * i;
         if (ug < G && u < nu) dpf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
     }
+    SLLM_TL(201);
     pdl_wait();
+    SLLM_TL(202);
 
     fused_prologue(a, xs, red, blockIdx.x == 0);
+    SLLM_TL(203);
     // gate / up rows of this block's hidden units: silu(g) * u, src/nn/swiglu.cpp:37-57
     for (int u = warp; u < nu; u += kFusedWarps) {
         float g, up;
@@ -358,6 +426,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         }
     }
     __syncthreads();
+    SLLM_TL(204);
     // share of the down-projection: y[n] = sum_u hid[u] * Wd[j0+u][n]
     if (ug < G) {
         float acc[EPC];
@@ -384,15 +453,23 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         for (int g = 1; g < G; ++g) s += s_y[(size_t)g * D + n];
         s_y[n] = s;
     }
+    SLLM_TL(205);
     cluster.sync();
+    SLLM_TL(206);
     // block c of the cluster adds up columns [c*D/8, (c+1)*D/8) of the 8 blocks, in rank order
     const int NR = D / kCS;
     for (int n = tid; n < NR; n += kFusedThreads) {
+        float t[kCS];
+#pragma unroll
+        for (int r = 0; r < kCS; ++r) t[r] = cluster.map_shared_rank(s_y, r)[c * NR + n];     // 8 loads in flight
         float s = 0.f;
-        for (int r = 0; r < kCS; ++r) s += cluster.map_shared_rank(s_y, r)[c * NR + n];
+#pragma unroll
+        for (int r = 0; r < kCS; ++r) s += t[r];
         a.parts_out[(size_t)(blockIdx.x / kCS) * D + c * NR + n] = s;
     }
+    SLLM_TL(207);
     cluster.sync();                              // peers may still be reading this block's shared memory
+    SLLM_TL(208);
 }
 
 // x[k] = base[k] + sum of partials, for callers that want the finished residual stream in one buffer
@@ -402,7 +479,13 @@ __global__ void __launch_bounds__(256) k_sum_parts(const float* __restrict__ bas
     pdl_wait();
     for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < D; k += gridDim.x * blockDim.x) {
         float v = base[k];
-        for (int p = 0; p < n_parts; ++p) v += __ldcg(parts + (size_t)p * D + k);
+        for (int p0 = 0; p0 < n_parts; p0 += 16) {
+            float t[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = (p0 + i < n_parts) ? __ldcg(parts + (size_t)(p0 + i) * D + k) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v += t[i];
+        }
         out[k] = v;
     }
 }

@@ -115,15 +115,18 @@ struct sllm_engine {
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
     unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
+    float* samp_w = nullptr; float* samp_pmax_val = nullptr; int* samp_pmax_idx = nullptr;
+    int samp_bps_cap = 128;
     // draws
     double* d_draws = nullptr; size_t draws_cap = 0;
     // host pinned
     int* h_flags = nullptr;
 
     // graphs
-    std::map<GraphKey, cudaGraphExec_t> graphs;
+    std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;   // exec + kernels per replay
 
     uint64_t launches = 0, decode_steps = 0;
+    int iter_launches = 0;             // kernels in the decode-iteration graph captured last
     float last_step_ms = 0.f;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     size_t max_dyn_smem = 0;
@@ -544,7 +547,9 @@ SampleArgs make_sample_args(sllm_engine* e, const sllm_sampling* o, int n_slots,
     s.temperature = o->temperature; s.top_p = o->top_p; s.penalty = o->repetition_penalty;
     s.eos = o->eos_token; s.stop_token = o->stop_token;
     s.draws = d_draws; s.n_slots = n_slots; s.draws_stride = stride; s.seeded = seeded;
-    s.g_mass = e->samp_mass; s.g_cnt = e->samp_cnt;
+    s.g_mass = e->samp_mass; s.g_cnt = e->samp_cnt; s.g_w = e->samp_w; s.g_pmax_val = e->samp_pmax_val; s.g_pmax_idx = e->samp_pmax_idx;
+    // blocks per slot of the two partial kernels: spread one slot over the GPU, many slots one block row each
+    s.bps = std::max(1, std::min(e->samp_bps_cap, (2 * e->sm_count) / std::max(1, n_slots)));
     s.next_tok_id = e->d_dec_id; s.next_tok_pos = e->d_dec_pos; s.next_tok_slot = e->d_dec_slot;
     return s;
 }
@@ -552,8 +557,8 @@ SampleArgs make_sample_args(sllm_engine* e, const sllm_sampling* o, int n_slots,
 int configure_kernels(sllm_engine* e) {
     // static shared memory of the sampler (histograms) counts against the same limit
     cudaFuncAttributes fa{};
-    CU(cudaFuncGetAttributes(&fa, k_sample));
-    CU(cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CU(cudaFuncGetAttributes(&fa, k_samp_pick));
+    CU(cudaFuncSetAttribute(k_samp_pick, cudaFuncAttributeMaxDynamicSharedMemorySize,
                             (int)(e->max_dyn_smem - fa.sharedSizeBytes)));
     if ((size_t)e->md.V * sizeof(float) + fa.sharedSizeBytes > e->max_dyn_smem)
         return fail(e, SLLM_ERR_INVALID, "vocab_size does not fit the sampler's shared memory");
@@ -561,10 +566,15 @@ int configure_kernels(sllm_engine* e) {
 }
 
 int launch_sampler(sllm_engine* e, const SampleArgs& s, bool pdl) {
-    const size_t smem = (size_t)e->md.V * sizeof(float);
-    int rc = set_smem(e, k_sample, smem);
+    const dim3 part_grid(s.bps, s.n_slots);
+    int rc = launch(e, k_samp_max, part_grid, dim3(kSampPartThreads), 0, pdl, s);
     if (rc) return rc;
-    return launch(e, k_sample, dim3(s.n_slots), dim3(kSampThreads), smem, pdl, s);
+    if (s.temperature > 0.0f) {
+        rc = launch(e, k_samp_hist, part_grid, dim3(kSampPartThreads), 0, pdl, s);
+        if (rc) return rc;
+    }
+    const size_t smem = s.temperature > 0.0f ? (size_t)e->md.V * sizeof(float) : 16;
+    return launch(e, k_samp_pick, dim3(s.n_slots), dim3(kSampThreads), smem, pdl, s);
 }
 
 // host bound on lengths: one more token per live slot per sampling step
@@ -593,7 +603,7 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* ou
     k.n_slots = s.n_slots; k.t = s.temperature; k.p = s.top_p; k.pen = s.penalty; k.eos = s.eos; k.stop = s.stop_token;
     k.seeded = s.seeded; k.stride = s.draws_stride; k.draws = s.draws;
     auto it = e->graphs.find(k);
-    if (it != e->graphs.end()) { *out = it->second; return SLLM_OK; }
+    if (it != e->graphs.end()) { *out = it->second.first; e->iter_launches = it->second.second; return SLLM_OK; }
     // run once outside capture so that every lazy attribute / module load has happened ...
     // (not needed for correctness of results: capture replays the same launches)
     cudaGraph_t g = nullptr;
@@ -601,6 +611,7 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* ou
     CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_iteration(e, s);
     cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    e->iter_launches = (int)(e->launches - before);
     e->launches = before;
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (ce != cudaSuccess) return fail(e, SLLM_ERR_CUDA, std::string("graph capture failed: ") + cudaGetErrorString(ce));
@@ -609,15 +620,15 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* ou
     cudaGraphDestroy(g);
     if (ce != cudaSuccess) return fail(e, SLLM_ERR_CUDA, std::string("graph instantiate failed: ") + cudaGetErrorString(ce));
     if (e->graphs.size() > 32) {
-        for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);
+        for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);
         e->graphs.clear();
     }
-    e->graphs[k] = ge;
+    e->graphs[k] = std::make_pair(ge, e->iter_launches);
     *out = ge;
     return SLLM_OK;
 }
 
-int launches_per_iteration(const sllm_engine* e) { return 1 + 5 * e->md.L + 1; }
+int launches_per_iteration(const sllm_engine* e) { return e->iter_launches; }
 
 int check_finished_flags(sllm_engine* e, bool* all_done, bool* nonfinite) {
     CU(cudaMemcpyAsync(e->h_flags, e->st.finished, e->n_live * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
@@ -636,7 +647,7 @@ int upload_draws(sllm_engine* e, const double* host, size_t n_slots, size_t stri
         if (e->d_draws) {
             CU(cudaStreamSynchronize(e->stream));
             cudaFree(e->d_draws);
-            for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);   // they hold the old pointer
+            for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);   // they hold the old pointer
             e->graphs.clear();
         }
         e->d_draws = nullptr;
@@ -713,13 +724,15 @@ int set_param_impl(sllm_engine* e, int idx, const float* host) {
     return SLLM_OK;
 }
 
-int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq) {
+int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, bool allow_long = false) {
     const ModelDims& m = e->md;
     if (n_seq == 0 || n_seq > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_CAPACITY, "n_seq exceeds max_batch");
     size_t total = 0;
     for (uint32_t s = 0; s < n_seq; ++s) {
         if (lens[s] == 0) return fail(e, SLLM_ERR_INVALID, "Inference::generate: prompt encoded to zero tokens");
-        if (lens[s] > (uint32_t)m.ctx) return fail(e, SLLM_ERR_INVALID, "Model::forward: seq_len exceeds context_length");
+        if (lens[s] > (uint32_t)(allow_long ? e->st.tok_cap - 1 : m.ctx))
+            return fail(e, SLLM_ERR_INVALID, allow_long ? "prompt longer than the engine's token buffer (2 x context_length)"
+                                                        : "Model::forward: seq_len exceeds context_length");
         total += lens[s];
     }
     for (size_t i = 0; i < total; ++i)
@@ -729,7 +742,7 @@ int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32
     // slot state on the device
     const int cap = e->st.tok_cap, words = m.V / 32;
     std::vector<uint32_t> toks((size_t)n_seq * cap, 0), seen((size_t)n_seq * words, 0);
-    std::vector<int> ntok(n_seq), zeros(n_seq, 0);
+    std::vector<int> ntok(n_seq), zeros(n_seq, 0), fin(n_seq, 0);
     size_t off = 0;
     for (uint32_t s = 0; s < n_seq; ++s) {
         for (uint32_t i = 0; i < lens[s]; ++i) {
@@ -740,7 +753,8 @@ int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32
         ntok[s] = (int)lens[s];
         off += lens[s];
         bool changed = false;
-        e->h_len_bound[s] = (int)lens[s];
+        e->h_len_bound[s] = std::min<int>((int)lens[s], m.ctx + 1);
+        fin[s] = lens[s] > (uint32_t)m.ctx ? 2 : 0;          // window already full: generation starts by sliding
         int rc = ensure_pages(e, (int)s, (int)lens[s], &changed);
         if (rc) return rc;
         rc = upload_block_table(e, (int)s);
@@ -749,7 +763,7 @@ int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32
     CU(cudaMemcpyAsync(e->st.tokens, toks.data(), toks.size() * 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaMemcpyAsync(e->st.seen, seen.data(), seen.size() * 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaMemcpyAsync(e->st.n_tok, ntok.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
-    CU(cudaMemcpyAsync(e->st.finished, zeros.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished, fin.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaMemcpyAsync(e->st.draw_idx, zeros.data(), n_seq * 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaStreamSynchronize(e->stream));
     return SLLM_OK;
@@ -785,7 +799,8 @@ int check_status(sllm_engine* e) {
 
 // Runs every prompt position through the model in chunks.  want_all: logits of every position go
 // to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
-int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits) {
+int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits,
+                 const int* slot_ids = nullptr) {
     const ModelDims& m = e->md;
     std::vector<uint32_t> c_id; std::vector<int> c_slot, c_pos, c_row; std::vector<int> c_row_dst;
     c_id.reserve(e->pass_cap); c_slot.reserve(e->pass_cap); c_pos.reserve(e->pass_cap);
@@ -822,8 +837,9 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
     for (uint32_t s = 0; s < n_seq; ++s) {
         for (uint32_t i = 0; i < lens[s]; ++i) {
             if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
-            if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back((int)s); }
-            c_id.push_back(ids[off + i]); c_slot.push_back((int)s); c_pos.push_back((int)i);
+            const int slot = slot_ids ? slot_ids[s] : (int)s;
+            if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
+            c_id.push_back(ids[off + i]); c_slot.push_back(slot); c_pos.push_back((int)i);
         }
         off += lens[s];
     }
@@ -976,7 +992,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
         A(&e->d_block_table, (size_t)e->max_batch * e->pages_per_seq, &e->scratch_bytes);
     }
     // slot state
-    e->st.tok_cap = m.ctx + 1;
+    e->st.tok_cap = 2 * m.ctx + 2;     // room for the window to slide by one context length
     A(&e->st.tokens, (size_t)e->max_batch * e->st.tok_cap, &e->scratch_bytes);
     A(&e->st.n_tok, e->max_batch, &e->scratch_bytes);
     A(&e->st.finished, e->max_batch, &e->scratch_bytes);
@@ -1009,6 +1025,9 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     }
     A(&e->samp_mass, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
     A(&e->samp_cnt, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
+    A(&e->samp_w, (size_t)e->max_batch * V, &e->scratch_bytes);
+    A(&e->samp_pmax_val, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);
+    A(&e->samp_pmax_idx, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);
     A(&e->d_status, 4, &e->scratch_bytes);
     if (!e->f32) {
         A(&e->xn16, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->att16, (size_t)e->pass_cap * D, &e->scratch_bytes);
@@ -1047,7 +1066,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
 void sllm_engine_destroy(sllm_engine* e) {
     if (!e) return;
     if (e->stream) cudaStreamSynchronize(e->stream);
-    for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);
     for (void* p : e->allocs) cudaFree(p);
     if (e->d_draws) cudaFree(e->d_draws);
     if (e->h_flags) cudaFreeHost(e->h_flags);
@@ -1321,9 +1340,10 @@ int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uin
     if (!e || !ids || !lens || !out || !out_lens) return fail(e, SLLM_ERR_INVALID, "sllm_generate: null argument");
     int rc = sampling_check(e, opt);
     if (rc) return rc;
-    rc = load_slots(e, ids, lens, n_seq);
+    rc = load_slots(e, ids, lens, n_seq, /*allow_long=*/true);
     if (rc) return rc;
     if (max_new > 0) {
+        const ModelDims& m = e->md;
         const double* dd = nullptr;
         int seeded = 0;
         if (opt->temperature > 0.0f) {
@@ -1338,10 +1358,53 @@ int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uin
             if (rc) return rc;
             dd = e->d_draws;
         }
-        rc = prefill_impl(e, ids, lens, n_seq, nullptr);
-        if (rc) return rc;
-        rc = decode_loop_impl(e, max_new, opt, dd, (int)max_new, seeded, false, nullptr);
-        if (rc) return rc;
+        // prompts that fit the window are prefilled; longer ones start in the sliding phase below
+        std::vector<uint32_t> fit_ids, fit_lens; std::vector<int> fit_slots;
+        size_t off = 0;
+        for (uint32_t s = 0; s < n_seq; ++s) {
+            if (lens[s] <= (uint32_t)m.ctx) {
+                fit_ids.insert(fit_ids.end(), ids + off, ids + off + lens[s]);
+                fit_lens.push_back(lens[s]); fit_slots.push_back((int)s);
+            }
+            off += lens[s];
+        }
+        if (!fit_lens.empty()) {
+            rc = prefill_impl(e, fit_ids.data(), fit_lens.data(), (uint32_t)fit_lens.size(), nullptr, fit_slots.data());
+            if (rc) return rc;
+            rc = decode_loop_impl(e, max_new, opt, dd, (int)max_new, seeded, false, nullptr);
+            if (rc) return rc;
+        }
+        // The window slides (src/inference.cpp:40-48): once a slot holds more than context_length tokens,
+        // every further token re-runs the last context_length tokens with positions restarting at 0, as
+        // the reference does for every token.  Penalty history and draw cursor live on the device and carry on.
+        SampleArgs sa = make_sample_args(e, opt, e->n_live, dd, (int)max_new, seeded);
+        std::vector<int> h_ntok(n_seq), h_fin(n_seq);
+        std::vector<uint32_t> window(m.ctx);
+        for (;;) {
+            CU(cudaMemcpyAsync(h_ntok.data(), e->st.n_tok, n_seq * 4, cudaMemcpyDeviceToHost, e->stream));
+            CU(cudaMemcpyAsync(h_fin.data(), e->st.finished, n_seq * 4, cudaMemcpyDeviceToHost, e->stream));
+            CU(cudaStreamSynchronize(e->stream));
+            bool any = false;
+            for (uint32_t s = 0; s < n_seq; ++s) {
+                const uint64_t made = (uint64_t)h_ntok[s] - lens[s];
+                if (h_fin[s] != 2 || made >= max_new || h_ntok[s] + 1 > e->st.tok_cap) continue;
+                CU(cudaMemcpyAsync(window.data(), e->st.tokens + (size_t)s * e->st.tok_cap + (h_ntok[s] - m.ctx), (size_t)m.ctx * 4,
+                                   cudaMemcpyDeviceToHost, e->stream));
+                CU(cudaStreamSynchronize(e->stream));
+                const uint32_t wl = (uint32_t)m.ctx; const int slot = (int)s, zero = 0;
+                rc = prefill_impl(e, window.data(), &wl, 1, nullptr, &slot);
+                if (rc) return rc;
+                CU(cudaMemcpyAsync(e->st.finished + s, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+                any = true;
+            }
+            if (!any) break;
+            rc = launch_sampler(e, sa, false);
+            if (rc) return rc;
+            bool all_done, nonfinite;
+            rc = check_finished_flags(e, &all_done, &nonfinite);
+            if (rc) return rc;
+            if (nonfinite) return fail(e, SLLM_ERR_NONFINITE, "Inference::generate: all logits are non-finite");
+        }
     }
     for (uint32_t s = 0; s < n_seq; ++s) {
         rc = sllm_get_tokens(e, s, out + (size_t)s * out_stride, out_stride, &out_lens[s]);
@@ -1445,5 +1508,19 @@ int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, co
                               reinterpret_cast<float*>(base + kStaticTicketBytes),
                               reinterpret_cast<unsigned int*>(base));
 }
+
+#ifdef SLLM_TIMELINE
+// debug builds only: copy out and reset the device-side timeline (pairs of id, globaltimer ns)
+int sllm_debug_timeline(unsigned long long* host, unsigned int cap_pairs, unsigned int* n) {
+    unsigned int cnt = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&cnt, g_tl_n, 4) != cudaSuccess) return SLLM_ERR_CUDA;
+    if (cnt > (1u << 15)) cnt = 1u << 15;
+    if (cnt > cap_pairs) cnt = cap_pairs;
+    if (cnt && cudaMemcpyFromSymbol(host, g_tl_buf, (size_t)cnt * 16) != cudaSuccess) return SLLM_ERR_CUDA;
+    cudaMemcpyToSymbol(g_tl_n, &zero, 4);
+    *n = cnt;
+    return SLLM_OK;
+}
+#endif
 
 }  // extern "C"

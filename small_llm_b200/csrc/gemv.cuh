@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
         }
     }
     pdl_wait();
+    if (MODE == kModeHead) SLLM_TL(400);
 
     // ---- prologue: activations to shared memory (+ RMSNorm) ---------------------------------
 #pragma unroll
@@ -92,9 +93,14 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
             else src = a.in + (size_t)ptok * K;
             for (int k = tid * 4; k < K; k += kGemvThreads * 4) {
                 float4 v = *reinterpret_cast<const float4*>(src + k);
-                for (int p = 0; p < a.n_parts; ++p) {          // fixed order: the sum is reproducible
-                    const float4 q = __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)p * K + k));
-                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                for (int p0 = 0; p0 < a.n_parts; p0 += 8) {    // 8 independent loads per round trip; fixed order of adds
+                    float4 q[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        q[i] = (p0 + i < a.n_parts) ? __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)(p0 + i) * K + k))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { v.x += q[i].x; v.y += q[i].y; v.z += q[i].z; v.w += q[i].w; }
                 }
                 *reinterpret_cast<float4*>(xs + t * K + k) = v;
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;

@@ -10,9 +10,15 @@
 // every weight >= 2^-24), so partial sums are associative and the result is independent of the
 // order in which threads add.  "The element at which the descending cumulative mass first reaches
 // a target" is found by bucket refinement over the weights' float bit patterns: a 1024-bucket
-// histogram of the whole key range (built once, while the weights are computed, and shared by both
-// queries), then <= 2 narrower histograms per query; ties (equal weights) go to the lower id.
-// Histogram mass is accumulated as three 16-bit limbs in 32-bit shared-memory atomics.
+// level-0 histogram (64 buckets per octave over the top 16 octaves, shared by both queries), then
+// <= 3 narrower histograms per query; ties (equal weights) go to the lower id.
+// Three kernels per sampling step, because one block can push only about one shared-memory atomic
+// per clock and a histogram of 32768 weights on a single SM therefore costs tens of microseconds:
+//   k_samp_max   (blocks_per_slot x n_slots blocks)  penalised scores, per-block first maximum
+//   k_samp_hist  (same grid)  weights expf((s - max)/T) to global memory, level-0 histogram by
+//                reductions in L2 (spread over all SMs and memory slices)
+//   k_samp_pick  (one block per slot)  top-p cut, draw, append, stop rules, next pass inputs
+// With temperature <= 0 only k_samp_max and k_samp_pick run.
 #pragma once
 #include "common.cuh"
 
@@ -43,11 +49,14 @@ struct SampleArgs {
     int draws_stride;
     int seeded;                   // 0: one entry per sampling step.  1: an entry is consumed only when at least
                                   //    two candidates are kept (std::discrete_distribution's behaviour)
-    // level-0 histogram in global memory: [n_slots][1024] mass and counts.  One block cannot push 32768 x 4
-    // atomics through its shared-memory atomic unit quickly (about one lane per clock); fire-and-forget
-    // reductions in L2 are spread over many memory slices.
+    // global scratch: level-0 histogram [n_slots][1024] (zero between steps), weights [n_slots][V],
+    // per-block maxima [n_slots][bps]
     unsigned long long* g_mass;
     unsigned int* g_cnt;
+    float* g_w;
+    float* g_pmax_val;
+    int* g_pmax_idx;
+    int bps;                      // blocks per slot in k_samp_max / k_samp_hist
     // next-pass token list, written for the decode step that follows
     uint32_t* next_tok_id;
     int* next_tok_pos;
@@ -96,20 +105,25 @@ struct SampScratch {
 
 struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned int cnt_above, ties, r; int found; };
 
-// Scans histogram h (keys lo..hi, bucket = (key-lo)>>sh) from the highest bucket down and picks the first
-// non-empty bucket at which cum + running mass reaches target.  Returns false when none does; then cum / cnt
-// have absorbed the whole range.  On success lo/hi shrink to the picked bucket and cum / cnt count what lies above.
-__device__ bool scan_pick(const SampHist& h, const unsigned long long* gm, const unsigned int* gc, SampScratch& s,
-                          unsigned long long target, uint32_t& lo, uint32_t& hi, int sh,
-                          unsigned long long& cum, unsigned int& cnt, unsigned long long& bucket_mass, unsigned int& bucket_cnt) {
+// Level-0 bucket of a weight key: 64 buckets per octave, bucket 1023 holds 1.0, bucket 0 everything below 2^-16.
+constexpr uint32_t kL0Shift = 17;
+constexpr uint32_t kL0Top = 0x3F800000u >> kL0Shift;          // 8128
+__device__ __forceinline__ int l0_bucket(uint32_t key) {
+    const int b = (int)(key >> kL0Shift) - (int)(kL0Top - (kSampBuckets - 1));
+    return b < 0 ? 0 : (b > kSampBuckets - 1 ? kSampBuckets - 1 : b);
+}
+__device__ __forceinline__ void l0_range(int b, uint32_t& lo, uint32_t& hi) {
+    lo = b == 0 ? 0u : ((uint32_t)(b + (int)kL0Top - (kSampBuckets - 1)) << kL0Shift);
+    hi = (((uint32_t)(b + (int)kL0Top - (kSampBuckets - 1)) + 1u) << kL0Shift) - 1u;
+}
+
+// Thread j holds bucket (top - j) of a histogram (my_m, my_c; zero when top - j < 0).  Picks the first
+// non-empty bucket, scanning from the highest, at which cum + running mass reaches target.  Returns the
+// picked bucket index or -1; cum / cnt absorb what lies above the pick (or everything when none is picked).
+__device__ int scan_pick(unsigned long long my_m, unsigned int my_c, int top, SampScratch& s, unsigned long long target,
+                         unsigned long long& cum, unsigned int& cnt, unsigned long long& bucket_mass, unsigned int& bucket_cnt) {
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
-    const int top = (int)((hi - lo) >> sh);
     const int b = top - tid;
-    unsigned long long my_m = 0; unsigned int my_c = 0;
-    if (b >= 0) {
-        if (gm) { my_m = __ldcg(gm + b); my_c = __ldcg(gc + b); }
-        else { my_m = hist_mass(h, b); my_c = h.cnt[b]; }
-    }
     unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -130,33 +144,30 @@ __device__ bool scan_pick(const SampHist& h, const unsigned long long* gm, const
     if (pick == kSampBuckets) {
         cum += s.tot_m; cnt += s.tot_c;
         __syncthreads();
-        return false;
+        return -1;
     }
     if (tid == pick) { s.pk_above_m = inc_m - my_m; s.pk_above_c = inc_c - my_c; s.pk_m = my_m; s.pk_c = my_c; }
     __syncthreads();
     cum += s.pk_above_m; cnt += s.pk_above_c;
     bucket_mass = s.pk_m; bucket_cnt = s.pk_c;
-    const uint32_t nlo = lo + ((uint32_t)(top - pick) << sh);
-    uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
-    if (nhi > hi) nhi = hi;
-    lo = nlo; hi = nhi;
     __syncthreads();
-    return true;
+    return top - pick;
 }
 
 // Finds the element, in descending (key, then ascending id) order, at which the running mass first reaches
-// `target`.  h0 is the histogram of the whole range [kmin, kmax] with shift sh0; h1 is working space.
-__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t kmin, uint32_t kmax, int sh0,
-                                    const unsigned long long* gm, const unsigned int* gc, SampHist& h1, SampScratch& s) {
+// `target`.  (l0_m, l0_c) is this thread's level-0 bucket (bucket 1023 - tid); h1 is working space.
+__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, unsigned long long l0_m, unsigned int l0_c,
+                                    SampHist& h1, SampScratch& s) {
     const int tid = threadIdx.x;
-    uint32_t lo = kmin, hi = kmax;
     unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
     SelectResult res;
-    res.found = 0; res.qk = 0; res.ties = 0; res.r = 0;
-    int sh = sh0;
-    for (int pass = 0; pass < 5; ++pass) {
-        if (pass > 0) {
-            sh = shift_for(hi - lo);
+    res.found = 0; res.qk = 0; res.ties = 0; res.r = 0; res.key = 0;
+    uint32_t lo = 0, hi = 0;
+    int b = scan_pick(l0_m, l0_c, kSampBuckets - 1, s, target, cum, cnt, bm, bc);
+    if (b >= 0) {
+        l0_range(b, lo, hi);
+        for (int pass = 0; pass < 4; ++pass) {
+            const int sh = shift_for(hi - lo);
             hist_clear(h1);
             __syncthreads();
             for (int i = tid; i < V; i += kSampThreads) {
@@ -164,20 +175,26 @@ __device__ SelectResult select_mass(const float* w, int V, unsigned long long ta
                 if (key >= lo && key <= hi) hist_add(h1, (int)((key - lo) >> sh), fix_of(w[i]));
             }
             __syncthreads();
-        }
-        if (!scan_pick(h1, pass == 0 ? gm : nullptr, gc, s, target, lo, hi, sh, cum, cnt, bm, bc)) break;
-        if (sh == 0) {                       // one key per bucket: done
-            res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
-            const unsigned long long need = target > cum ? target - cum : 0;
-            unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
-            if (r < 1) r = 1;
-            if (r > bc) r = bc;
-            res.r = (unsigned int)r;
-            break;
+            const int top = (int)((hi - lo) >> sh);
+            const int bb = top - tid;
+            b = scan_pick(bb >= 0 ? hist_mass(h1, bb) : 0ull, bb >= 0 ? h1.cnt[bb] : 0u, top, s, target, cum, cnt, bm, bc);
+            if (b < 0) break;                    // cannot happen: the parent bucket contained the crossing
+            const uint32_t nlo = lo + ((uint32_t)b << sh);
+            uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
+            if (nhi > hi) nhi = hi;
+            lo = nlo; hi = nhi;
+            if (sh == 0) {                       // one key per bucket: done
+                res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
+                const unsigned long long need = target > cum ? target - cum : 0;
+                unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
+                if (r < 1) r = 1;
+                if (r > bc) r = bc;
+                res.r = (unsigned int)r;
+                break;
+            }
         }
     }
     res.cum_above = cum; res.cnt_above = cnt;
-    if (!res.found) res.key = lo;
     return res;
 }
 
@@ -212,131 +229,182 @@ __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r,
     return out;
 }
 
-__global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
-    extern __shared__ __align__(16) float w[];                 // [V] scores, then weights
+
+constexpr int kSampPartThreads = 256;
+
+__device__ __forceinline__ float penalised(const SampleArgs& a, const float* lg, const uint32_t* seen, int i) {
+    float s = lg[i];
+    if (a.penalty != 1.0f && ((seen[i >> 5] >> (i & 31)) & 1u)) s = s > 0.f ? s / a.penalty : s * a.penalty;
+    return s;
+}
+__device__ __forceinline__ void first_max(float& bv, int& bi, float v2, int i2) {
+    if (v2 > bv || (v2 == bv && i2 < bi)) { bv = v2; bi = i2; }
+}
+
+// per-block first maximum of the penalised scores: grid (bps, n_slots)
+__global__ void __launch_bounds__(kSampPartThreads) k_samp_max(const SampleArgs a) {
+    __shared__ float r_val[kSampPartThreads / 32];
+    __shared__ int r_idx[kSampPartThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    SLLM_TL(300);
+    const int slot = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int per = (a.V + a.bps - 1) / a.bps, b0 = blockIdx.x * per, b1 = min(a.V, b0 + per);
+    const float* lg = a.logits + (size_t)slot * a.V;
+    const uint32_t* seen = a.st.seen + (size_t)slot * (a.V / 32);
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int i = b0 + tid; i < b1; i += kSampPartThreads) {
+        const float s = penalised(a, lg, seen, i);
+        if (s > bv) { bv = s; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first_max(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) { r_val[wp] = bv; r_idx[wp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < kSampPartThreads / 32; ++w) first_max(bv, bi, r_val[w], r_idx[w]);
+        a.g_pmax_val[(size_t)slot * a.bps + blockIdx.x] = bv;
+        a.g_pmax_idx[(size_t)slot * a.bps + blockIdx.x] = bi;
+    }
+}
+
+// the slot's maximum from the per-block maxima (every thread of the block calls it; needs one __syncthreads pair)
+__device__ __forceinline__ void slot_max(const SampleArgs& a, int slot, float* s_val, int* s_idx, float& mx, int& arg) {
+    const int tid = threadIdx.x;
+    if (tid < 32) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int b = tid; b < a.bps; b += 32)
+            first_max(bv, bi, __ldcg(a.g_pmax_val + (size_t)slot * a.bps + b), __ldcg(a.g_pmax_idx + (size_t)slot * a.bps + b));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) first_max(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (tid == 0) { *s_val = bv; *s_idx = bi; }
+    }
+    __syncthreads();
+    mx = *s_val; arg = *s_idx;
+}
+
+// weights and level-0 histogram: grid (bps, n_slots)
+__global__ void __launch_bounds__(kSampPartThreads) k_samp_hist(const SampleArgs a) {
+    __shared__ float s_val; __shared__ int s_idx;
+    pdl_launch_dependents();
+    pdl_wait();
+    SLLM_TL(310);
+    const int slot = blockIdx.y, tid = threadIdx.x;
+    if (a.st.finished[slot]) return;
+    float mx; int arg;
+    slot_max(a, slot, &s_val, &s_idx, mx, arg);
+    if (!isfinite(mx)) return;
+    const int per = (a.V + a.bps - 1) / a.bps, b0 = blockIdx.x * per, b1 = min(a.V, b0 + per);
+    const float* lg = a.logits + (size_t)slot * a.V;
+    const uint32_t* seen = a.st.seen + (size_t)slot * (a.V / 32);
+    float* w = a.g_w + (size_t)slot * a.V;
+    unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
+    unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
+    for (int i = b0 + tid; i < b1; i += kSampPartThreads) {
+        const float e = expf((penalised(a, lg, seen, i) - mx) / a.temperature);
+        w[i] = e;
+        const int b = l0_bucket(__float_as_uint(e));
+        atomicAdd(gm + b, fix_of(e));              // results unused: reductions performed in L2
+        atomicAdd(gc + b, 1u);
+    }
+}
+
+// one block per slot: top-p cut, draw, append, stop rules, inputs of the next decode pass
+__global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) {
+    extern __shared__ __align__(16) float w[];                 // [V] weights
     __shared__ SampHist h1;
     __shared__ SampScratch sc;
-    __shared__ float r_val[32];
-    __shared__ int r_idx[32];
     __shared__ unsigned long long r_sum[32];
-    __shared__ uint32_t r_kmin[32];
     __shared__ unsigned int s_scan[32];
     __shared__ int s_out;
-    __shared__ float s_max; __shared__ int s_arg;
-    __shared__ unsigned long long s_total; __shared__ uint32_t s_kmin;
+    __shared__ float s_val; __shared__ int s_idx;
+    __shared__ unsigned long long s_total;
 
     const int slot = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int V = a.V;
-
-    pdl_launch_dependents();        // successors may start fetching their weights now
+    pdl_launch_dependents();
     pdl_wait();
 
+    SLLM_TL(320);
     int n_tok = a.st.n_tok[slot];
     const int fin = a.st.finished[slot];
     int token = -1;
-    unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
-    unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
-    for (int b = tid; b < kSampBuckets; b += kSampThreads) { gm[b] = 0ull; gc[b] = 0u; }
-
     if (!fin) {
-        const float* lg = a.logits + (size_t)slot * V;
-        const uint32_t* seen = a.st.seen + (size_t)slot * (V / 32);
-        // ---- penalty + first maximum --------------------------------------------------------
-        float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int i = tid; i < V; i += kSampThreads) {
-            float s = lg[i];
-            if (a.penalty != 1.0f && ((seen[i >> 5] >> (i & 31)) & 1u)) s = s > 0.f ? s / a.penalty : s * a.penalty;
-            w[i] = s;
-            if (s > bv) { bv = s; bi = i; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (v2 > bv || (v2 == bv && i2 < bi)) { bv = v2; bi = i2; }
-        }
-        if (lane == 0) { r_val[wp] = bv; r_idx[wp] = bi; }
-        __syncthreads();
-        if (wp == 0) {
-            bv = r_val[lane]; bi = r_idx[lane];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (v2 > bv || (v2 == bv && i2 < bi)) { bv = v2; bi = i2; }
-            }
-            if (lane == 0) { s_max = bv; s_arg = bi; }
-        }
-        __syncthreads();
-        const float mx = s_max;
+        float mx; int arg;
+        slot_max(a, slot, &s_val, &s_idx, mx, arg);
         if (!isfinite(mx)) {
             if (tid == 0) a.st.finished[slot] = 3;
         } else if (a.temperature <= 0.0f) {
-            token = s_arg;
+            token = arg;
         } else {
-            // ---- weights, total mass, smallest key ---------------------------------------------
-            unsigned long long sum = 0; uint32_t kmin = 0xffffffffu;
-            for (int i = tid; i < V; i += kSampThreads) {
-                const float e = expf((w[i] - mx) / a.temperature);
-                w[i] = e;
-                sum += fix_of(e);
-                kmin = min(kmin, __float_as_uint(e));
-            }
+            unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
+            unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
+            // this thread's level-0 bucket (descending order: thread 0 holds the bucket of weight 1.0)
+            const int b0 = kSampBuckets - 1 - tid;
+            const unsigned long long l0_m = __ldcg(gm + b0);
+            const unsigned int l0_c = __ldcg(gc + b0);
+            gm[b0] = 0ull; gc[b0] = 0u;                        // ready for the next step
+            const float* gw = a.g_w + (size_t)slot * V;
+            for (int base = 0; base < V; base += kSampThreads * 4 * 8) {      // 8 independent 16-byte loads per thread and trip
+                float4 t[8];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base + (j * kSampThreads + tid) * 4;
+                    t[j] = i < V ? __ldcg(reinterpret_cast<const float4*>(gw + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base + (j * kSampThreads + tid) * 4;
+                    if (i < V) *reinterpret_cast<float4*>(w + i) = t[j];
+                }
             }
-            if (lane == 0) { r_sum[wp] = sum; r_kmin[wp] = kmin; }
+            unsigned long long sum = l0_m;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) r_sum[wp] = sum;
             __syncthreads();
-            if (tid == 0) {
-                unsigned long long t = 0; uint32_t k = 0xffffffffu;
-                for (int i = 0; i < 32; ++i) { t += r_sum[i]; k = min(k, r_kmin[i]); }
-                s_total = t; s_kmin = k;
-            }
+            if (tid == 0) { unsigned long long t = 0; for (int i = 0; i < 32; ++i) t += r_sum[i]; s_total = t; }
             __syncthreads();
             const unsigned long long total = s_total;
-            const uint32_t klo = s_kmin;
-            const uint32_t kmax = __float_as_uint(1.0f);      // the maximum's weight is exp(0) = 1
-            // histogram of the whole key range, used by both queries
-            const int sh0 = shift_for(kmax - klo);
-            for (int i = tid; i < V; i += kSampThreads) {
-                const float e = w[i];
-                const int b = (int)((__float_as_uint(e) - klo) >> sh0);
-                atomicAdd(gm + b, fix_of(e));                  // results are not used: compiled to reductions
-                atomicAdd(gc + b, 1u);
-            }
-            __threadfence();
-            __syncthreads();
+            SLLM_TL(322);
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
-            const SelectResult cut = select_mass(w, V, t1, klo, kmax, sh0, gm, gc, h1, sc);
+            const SelectResult cut = select_mass(w, V, t1, l0_m, l0_c, h1, sc);
             unsigned long long kept_mass; unsigned int kept;
             if (cut.found) { kept_mass = cut.cum_above + (unsigned long long)cut.r * cut.qk; kept = cut.cnt_above + cut.r; }
             else { kept_mass = cut.cum_above; kept = cut.cnt_above; }
+            SLLM_TL(323);
             // ---- the draw -------------------------------------------------------------------------
             double u = 0.0;
             if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
-            const SelectResult hit = select_mass(w, V, t2, klo, kmax, sh0, gm, gc, h1, sc);
+            const SelectResult hit = select_mass(w, V, t2, l0_m, l0_c, h1, sc);
             uint32_t key; unsigned int r;
             if (hit.found && (hit.cnt_above + hit.r) <= kept) { key = hit.key; r = hit.r; }
             else if (cut.found) { key = cut.key; r = cut.r; }                  // last kept candidate
-            else { key = klo; r = 0xffffffffu; }
-            if (r == 0xffffffffu) {                                            // last of everything: highest id of the smallest key
+            else {                                                             // last of everything: highest id of the smallest weight
+                uint32_t kmin = 0xffffffffu;
+                for (int i = tid; i < V; i += kSampThreads) kmin = min(kmin, __float_as_uint(w[i]));
+                kmin = __reduce_min_sync(0xffffffffu, kmin);
+                if (lane == 0) s_scan[wp] = kmin;
+                __syncthreads();
+                for (int i = 0; i < 32; ++i) kmin = min(kmin, s_scan[i]);
+                __syncthreads();
                 unsigned int c = 0;
-                for (int i = tid; i < V; i += kSampThreads) c += (__float_as_uint(w[i]) == key);
+                for (int i = tid; i < V; i += kSampThreads) c += (__float_as_uint(w[i]) == kmin);
                 c = __reduce_add_sync(0xffffffffu, c);
                 if (lane == 0) s_scan[wp] = c;
                 __syncthreads();
                 unsigned int t = 0;
                 for (int i = 0; i < 32; ++i) t += s_scan[i];
                 __syncthreads();
-                r = t;
+                key = kmin; r = t;
             }
+            SLLM_TL(324);
             token = nth_with_key(w, V, key, r, s_scan, &s_out);
+            SLLM_TL(325);
             if (tid == 0 && (!a.seeded || kept >= 2)) a.st.draw_idx[slot] += 1;
         }
     }
@@ -360,6 +428,7 @@ __global__ void __launch_bounds__(kSampThreads) k_sample(const SampleArgs a) {
         a.next_tok_pos[slot] = p;
         a.next_tok_slot[slot] = slot;
     }
+    SLLM_TL(321);
 }
 
 }  // namespace sllm

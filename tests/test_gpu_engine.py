@@ -141,14 +141,31 @@ def test_seeded_mode_reproduces_reference_loop(golden_dir):
     import os
     g = np.load(os.path.join(golden_dir, "small_ref.npz"))
     o, eng = make_pair(SMALL, seed=3, stddev=0.2, fp32=True)
-    for seed in (2, 1234):
+    for seed in (2, 1234, 3):
         t, p, pen, n = g[f"opts_seed{seed}"]
         ref = g[f"stream_seed{seed}"]
         opt = SamplingOptions(temperature=float(t), top_p=float(p), repetition_penalty=float(pen), seed=seed)
-        n_fit = min(int(n), SMALL.context + 1 - len(g["prompt"]))     # engine stops at the context limit
-        got = eng.generate([g["prompt"]], n_fit, opt, draws=None, eos=SMALL_EOS)[0]
-        assert np.array_equal(got, ref[: len(got)]), seed
-        assert len(got) == min(len(ref), len(g["prompt"]) + n_fit)
+        got = eng.generate([g["prompt"]], int(n), opt, draws=None, eos=SMALL_EOS)[0]
+        assert np.array_equal(got, ref), seed
+    assert len(g["stream_seed2"]) > SMALL.context + 1          # these streams slid the window, as the reference does
+
+
+def test_sliding_window_and_long_prompt_match_oracle():
+    """Beyond context_length the reference re-runs the last context_length tokens for every new token
+    (positions restart at 0); prompts longer than the context are windowed the same way."""
+    cfg = SMALL
+    o, eng = make_pair(cfg, seed=3, stddev=0.2, fp32=True, max_batch=2)
+    us = uniforms(7, 30)
+    opt = SamplingOptions(temperature=0.9, top_p=0.9, repetition_penalty=1.2)
+    long_prompt = prompt_ids(11, cfg.context + 9, cfg.vocab)
+    short_prompt = prompt_ids(12, cfg.context - 3, cfg.vocab)
+    draws = np.repeat(us.astype(np.float64).reshape(-1, 1), 2, axis=1)
+    got = eng.generate([long_prompt, short_prompt], 30, opt, draws=draws, eos=SMALL_EOS)
+    for p, gs in zip((long_prompt, short_prompt), got):
+        ref = o.generate(p, 30, 0.9, 0.9, 1.2, us=us, eos=SMALL_EOS)
+        assert np.array_equal(gs, ref)
+    with pytest.raises(ValueError, match="token buffer"):
+        eng.generate([prompt_ids(1, 2 * cfg.context + 2, cfg.vocab)], 1, opt, draws=draws[:1], eos=SMALL_EOS)
 
 
 def test_stop_rules_and_errors():
