@@ -51,35 +51,40 @@ struct FusedArgs {
 };
 
 // x = x_in (+ partial sums), stored as the new residual by the designated block; xs = RMSNorm(x) * gain.
-__device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, float* red, bool store) {
+// The 1 + n_parts source vectors are split into up to 3 groups of threads, each thread requests its group's
+// 16-byte pieces together (one round trip to L2 for up to 10 sources), the groups are combined in shared
+// memory in a fixed order.  `scratch` holds 2 * D floats.
+__device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, float* scratch, float* red, bool store) {
     const int D = a.m.D, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* base = a.emb ? a.emb + (size_t)a.tok_id[0] * D : a.x_in;
-    float ss = 0.f;
-    // two elements per thread and up to 12 partials each are requested together (one round trip to L2),
-    // then added in a fixed order
-    for (int k0 = tid; k0 < D; k0 += 2 * kFusedThreads) {
-        const int k1 = k0 + kFusedThreads;
-        const bool has1 = k1 < D;
-        float v0 = base[k0], v1 = has1 ? base[k1] : 0.f;
-        for (int p0 = 0; p0 < a.n_parts_in; p0 += 12) {
-            float t0[12], t1[12];
+    const int nch = D / 4;
+    const int ng = max(1, min(3, kFusedThreads / nch));
+    const int nsrc = 1 + a.n_parts_in, per = (nsrc + ng - 1) / ng;
+    for (int item = tid; item < ng * nch; item += kFusedThreads) {
+        const int g = item / nch, c = item - g * nch;
+        const int s_end = min(nsrc, (g + 1) * per);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = g * per; s0 < s_end; s0 += 10) {
+            float4 t[10];
 #pragma unroll
-            for (int i = 0; i < 12; ++i) {
-                const bool ok = p0 + i < a.n_parts_in;
-                t0[i] = ok ? __ldcg(a.parts_in + (size_t)(p0 + i) * D + k0) : 0.f;
-                t1[i] = ok && has1 ? __ldcg(a.parts_in + (size_t)(p0 + i) * D + k1) : 0.f;
+            for (int i = 0; i < 10; ++i) {
+                const int sidx = s0 + i;
+                const float* src = sidx == 0 ? base : a.parts_in + (size_t)(sidx - 1) * D;
+                t[i] = sidx < s_end ? __ldcg(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int i = 0; i < 12; ++i) { v0 += t0[i]; v1 += t1[i]; }
+            for (int i = 0; i < 10; ++i) { acc.x += t[i].x; acc.y += t[i].y; acc.z += t[i].z; acc.w += t[i].w; }
         }
-        xs[k0] = v0;
-        ss += v0 * v0;
-        if (store) a.x_out[k0] = v0;
-        if (has1) {
-            xs[k1] = v1;
-            ss += v1 * v1;
-            if (store) a.x_out[k1] = v1;
-        }
+        *reinterpret_cast<float4*>((g == 0 ? xs : scratch + (size_t)(g - 1) * D) + c * 4) = acc;
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int k = tid; k < D; k += kFusedThreads) {
+        float v = xs[k];
+        for (int g = 1; g < ng; ++g) v += scratch[(size_t)(g - 1) * D + k];
+        xs[k] = v;
+        ss += v * v;
+        if (store) a.x_out[k] = v;
     }
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
     static_assert(RP >= 2 && RP % 2 == 0, "head_dim must give each block whole RoPE pairs");
     static_assert(kFusedThreads % DP == 0 && LPK <= 32, "unsupported head_dim");
 
-    extern __shared__ __align__(16) float xs[];          // [D]
+    extern __shared__ __align__(16) float xs[];          // [D] + 2 * D of prologue scratch
     __shared__ float red[kFusedWarps];
     __shared__ float s_q[HD], s_k[HD], s_v[HD];          // filled by all 8 blocks of the head
     __shared__ float s_part[kCS][HD + 2];                // (out[HD], max, sum) of every block
@@ -196,7 +201,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
     const int n_pages = pos / kPage + 1;
     const int page_new = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
     const int page_first = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + min(c, n_pages - 1)];
-    fused_prologue(a, xs, red, c == 0 && head == 0);
+    fused_prologue(a, xs, xs + D, red, c == 0 && head == 0);
     SLLM_TL(103);
     for (int pi = warp; pi < NP; pi += kFusedWarps) {
         const int row = pair_row(pi);
@@ -414,7 +419,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
     pdl_wait();
     SLLM_TL(202);
 
-    fused_prologue(a, xs, red, blockIdx.x == 0);
+    fused_prologue(a, xs, s_y, red, blockIdx.x == 0);
     SLLM_TL(203);
     // gate / up rows of this block's hidden units: silu(g) * u, src/nn/swiglu.cpp:37-57
     for (int u = warp; u < nu; u += kFusedWarps) {

@@ -428,7 +428,7 @@ int launch_cluster(sllm_engine* e, void (*kern)(KArgs...), dim3 grid, size_t sme
 template <typename WT, int PF>
 int launch_attn_block(sllm_engine* e, const FusedArgs& a, bool pdl) {
     const dim3 grid(kCS, a.m.H);
-    const size_t smem = (size_t)a.m.D * sizeof(float);
+    const size_t smem = (size_t)3 * a.m.D * sizeof(float);
     switch (a.m.hd) {
         case 16: return launch_cluster(e, k_attn_block<WT, 16, PF>, grid, smem, pdl, a);
         case 32: return launch_cluster(e, k_attn_block<WT, 32, PF>, grid, smem, pdl, a);
@@ -443,7 +443,7 @@ int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logi
     const ModelDims& m = e->md;
     const int chunks_per_lane = (m.D / Elems<WT>::per16 + 31) / 32;
     const int G = kFusedThreads / (m.D / Elems<WT>::per16);
-    const size_t smem_b = (size_t)(1 + G) * m.D * sizeof(float);
+    const size_t smem_b = (size_t)(1 + std::max(G, 2)) * m.D * sizeof(float);
     const int ncl = e->fused_nb / kCS;
     FusedArgs a{};
     a.m = m; a.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
@@ -1014,7 +1014,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
         e->fused_upc = std::max<int>((int)((F + 143) / 144), 2);
         e->fused_nb = (int)(((F + e->fused_upc - 1) / e->fused_upc + kCS - 1) / kCS) * kCS;
         e->fused_ok = nch <= kFusedThreads && e->fused_upc <= 64 && D % kCS == 0 &&
-                      (size_t)(1 + kFusedThreads / nch) * D * sizeof(float) <= 48 * 1024;
+                      (size_t)(1 + std::max(kFusedThreads / nch, 2)) * D * sizeof(float) <= 48 * 1024;
         if (e->fused_ok) {
             A(&e->xb, D, &e->scratch_bytes);
             A(&e->attn_parts, H * D, &e->scratch_bytes);

@@ -93,14 +93,14 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
             else src = a.in + (size_t)ptok * K;
             for (int k = tid * 4; k < K; k += kGemvThreads * 4) {
                 float4 v = *reinterpret_cast<const float4*>(src + k);
-                for (int p0 = 0; p0 < a.n_parts; p0 += 8) {    // 8 independent loads per round trip; fixed order of adds
-                    float4 q[8];
+                for (int p0 = 0; p0 < a.n_parts; p0 += 10) {   // 10 independent loads per round trip; fixed order of adds
+                    float4 q[10];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
+                    for (int i = 0; i < 10; ++i)
                         q[i] = (p0 + i < a.n_parts) ? __ldcg(reinterpret_cast<const float4*>(a.parts + (size_t)(p0 + i) * K + k))
                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) { v.x += q[i].x; v.y += q[i].y; v.z += q[i].z; v.w += q[i].w; }
+                    for (int i = 0; i < 10; ++i) { v.x += q[i].x; v.y += q[i].y; v.z += q[i].z; v.w += q[i].w; }
                 }
                 *reinterpret_cast<float4*>(xs + t * K + k) = v;
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;

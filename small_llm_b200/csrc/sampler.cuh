@@ -198,30 +198,34 @@ __device__ SelectResult select_mass(const float* w, int V, unsigned long long ta
     return res;
 }
 
-// id of the r-th (1-based) lowest index whose weight has bit pattern `key`
+// id of the r-th (1-based) lowest index whose weight has bit pattern `key`.  Warp w owns a contiguous block of
+// ids and walks it 32 at a time (conflict-free shared-memory reads); ballots keep the order by id.
 __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r, unsigned int* s_scan, int* s_out) {
-    const int tid = threadIdx.x;
-    const int per = (V + kSampThreads - 1) / kSampThreads;
-    const int b = tid * per, e = min(V, b + per);
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int per_warp = ((V + 31) / 32 + 31) / 32 * 32;       // ids per warp, a multiple of 32
+    const int b = wp * per_warp, e = min(V, b + per_warp);
     unsigned int c = 0;
-    for (int i = b; i < e; ++i) c += (__float_as_uint(w[i]) == key);
-    unsigned int inc = c;
-    const int lane = tid & 31, wp = tid >> 5;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += c2;
+    for (int i = b; i < e; i += 32) {
+        const bool m = (i + lane < e) && __float_as_uint(w[i + lane]) == key;
+        c += __popc(__ballot_sync(0xffffffffu, m));
     }
-    if (lane == 31) s_scan[wp] = inc;
+    if (lane == 0) s_scan[wp] = c;
     if (tid == 0) *s_out = -1;
     __syncthreads();
-    unsigned int off = 0;
-    for (int k = 0; k < wp; ++k) off += s_scan[k];
-    const unsigned int before = off + inc - c;
-    if (c > 0 && r > before && r <= before + c) {
-        unsigned int seen = before;
-        for (int i = b; i < e; ++i)
-            if (__float_as_uint(w[i]) == key && ++seen == r) { *s_out = i; break; }
+    unsigned int before = 0;
+    for (int k = 0; k < wp; ++k) before += s_scan[k];
+    if (c > 0 && r > before && r <= before + c) {              // warp-uniform
+        unsigned int rr = r - before;
+        for (int i = b; i < e; i += 32) {
+            const bool m = (i + lane < e) && __float_as_uint(w[i + lane]) == key;
+            const unsigned int bal = __ballot_sync(0xffffffffu, m);
+            const unsigned int n = __popc(bal);
+            if (rr <= n) {
+                if (lane == 0) *s_out = i + (int)__fns(bal, 0, (int)rr);
+                break;
+            }
+            rr -= n;
+        }
     }
     __syncthreads();
     const int out = *s_out;
@@ -229,6 +233,90 @@ __device__ int nth_with_key(const float* w, int V, uint32_t key, unsigned int r,
     return out;
 }
 
+// Exact answer inside one level-0 bucket when it holds at most kSampCand elements: gather them, order them by
+// (weight descending, id ascending) by rank counting, running mass by a block scan.  Returns the position of the
+// crossing element in that order (or -1), its id, and the mass / count up to and including it.
+constexpr int kSampCand = 1024;
+struct CandScratch {
+    uint32_t key[kSampCand], skey[kSampCand];
+    int id[kSampCand], sid[kSampCand];
+    unsigned long long warp_m[32];
+    int n, pick;
+};
+__device__ int cand_solve(const float* w, int V, uint32_t lo, uint32_t hi, unsigned int n_expect, unsigned long long need,
+                          CandScratch& cs, int& id_out, unsigned long long& mass_incl, unsigned int& cnt_incl) {
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    if (tid == 0) { cs.n = 0; cs.pick = kSampCand; }
+    __syncthreads();
+    for (int i = tid; i < V; i += kSampThreads) {
+        const uint32_t k = __float_as_uint(w[i]);
+        if (k >= lo && k <= hi) {
+            const int p = atomicAdd(&cs.n, 1);
+            if (p < kSampCand) { cs.key[p] = k; cs.id[p] = i; }
+        }
+    }
+    __syncthreads();
+    const int n = min(cs.n, kSampCand);
+    (void)n_expect;
+    uint32_t mk = 0; int mi = 0;
+    if (tid < n) {
+        mk = cs.key[tid]; mi = cs.id[tid];
+        int rank = 0;
+        for (int j = 0; j < n; ++j) {
+            const uint32_t kj = cs.key[j];
+            rank += (kj > mk) || (kj == mk && cs.id[j] < mi);
+        }
+        cs.skey[rank] = mk; cs.sid[rank] = mi;
+    }
+    __syncthreads();
+    unsigned long long q = tid < n ? fix_of(__uint_as_float(cs.skey[tid])) : 0ull;
+    unsigned long long inc = q;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long m2 = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += m2;
+    }
+    if (lane == 31) cs.warp_m[wp] = inc;
+    __syncthreads();
+    unsigned long long off = 0;
+    for (int k = 0; k < wp; ++k) off += cs.warp_m[k];
+    inc += off;
+    if (tid < n && inc >= need) atomicMin(&cs.pick, tid);
+    __syncthreads();
+    const int pick = cs.pick;
+    __shared__ unsigned long long s_mass;
+    if (pick < kSampCand && tid == pick) s_mass = inc;
+    __syncthreads();
+    if (pick >= kSampCand) return -1;
+    id_out = cs.sid[pick];
+    mass_incl = s_mass;
+    cnt_incl = (unsigned int)pick + 1u;
+    __syncthreads();
+    return pick;
+}
+
+// Where the descending running mass first reaches `target`: through the candidate solver when the level-0
+// bucket is small enough (the usual case), else through the histogram refinement.
+struct Loc { int found, have_id, id; unsigned long long mass_incl; unsigned int cnt_incl; uint32_t key; unsigned int r; };
+__device__ Loc locate(const float* w, int V, unsigned long long target, unsigned long long l0_m, unsigned int l0_c,
+                      SampHist& h1, SampScratch& sc, CandScratch& cs) {
+    Loc L; L.found = 0; L.have_id = 0; L.id = -1; L.key = 0; L.r = 0;
+    unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
+    const int b = scan_pick(l0_m, l0_c, kSampBuckets - 1, sc, target, cum, cnt, bm, bc);
+    if (b < 0) { L.mass_incl = cum; L.cnt_incl = cnt; return L; }
+    if (bc <= (unsigned int)kSampCand) {
+        uint32_t lo, hi;
+        l0_range(b, lo, hi);
+        unsigned long long m = 0; unsigned int c = 0; int id = -1;
+        const int pick = cand_solve(w, V, lo, hi, bc, target > cum ? target - cum : 0ull, cs, id, m, c);
+        if (pick >= 0) { L.found = 1; L.have_id = 1; L.id = id; L.mass_incl = cum + m; L.cnt_incl = cnt + c; return L; }
+    }
+    const SelectResult r = select_mass(w, V, target, l0_m, l0_c, h1, sc);
+    L.found = r.found; L.key = r.key; L.r = r.r;
+    L.mass_incl = r.found ? r.cum_above + (unsigned long long)r.r * r.qk : r.cum_above;
+    L.cnt_incl = r.found ? r.cnt_above + r.r : r.cnt_above;
+    return L;
+}
 
 constexpr int kSampPartThreads = 256;
 
@@ -314,6 +402,7 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
     extern __shared__ __align__(16) float w[];                 // [V] weights
     __shared__ SampHist h1;
     __shared__ SampScratch sc;
+    __shared__ CandScratch cs;
     __shared__ unsigned long long r_sum[32];
     __shared__ unsigned int s_scan[32];
     __shared__ int s_out;
@@ -370,21 +459,21 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
-            const SelectResult cut = select_mass(w, V, t1, l0_m, l0_c, h1, sc);
-            unsigned long long kept_mass; unsigned int kept;
-            if (cut.found) { kept_mass = cut.cum_above + (unsigned long long)cut.r * cut.qk; kept = cut.cnt_above + cut.r; }
-            else { kept_mass = cut.cum_above; kept = cut.cnt_above; }
+            const Loc cut = locate(w, V, t1, l0_m, l0_c, h1, sc, cs);
+            const unsigned long long kept_mass = cut.mass_incl;
+            const unsigned int kept = cut.cnt_incl;
             SLLM_TL(323);
             // ---- the draw -------------------------------------------------------------------------
             double u = 0.0;
             if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
-            const SelectResult hit = select_mass(w, V, t2, l0_m, l0_c, h1, sc);
-            uint32_t key; unsigned int r;
-            if (hit.found && (hit.cnt_above + hit.r) <= kept) { key = hit.key; r = hit.r; }
-            else if (cut.found) { key = cut.key; r = cut.r; }                  // last kept candidate
-            else {                                                             // last of everything: highest id of the smallest weight
+            const Loc hit = locate(w, V, t2, l0_m, l0_c, h1, sc, cs);
+            SLLM_TL(324);
+            const Loc& use = (hit.found && hit.cnt_incl <= kept) ? hit : cut;    // else: the last kept candidate
+            if (use.found) {
+                token = use.have_id ? use.id : nth_with_key(w, V, use.key, use.r, s_scan, &s_out);
+            } else {                                                             // last of everything: highest id of the smallest weight
                 uint32_t kmin = 0xffffffffu;
                 for (int i = tid; i < V; i += kSampThreads) kmin = min(kmin, __float_as_uint(w[i]));
                 kmin = __reduce_min_sync(0xffffffffu, kmin);
@@ -400,10 +489,8 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
                 unsigned int t = 0;
                 for (int i = 0; i < 32; ++i) t += s_scan[i];
                 __syncthreads();
-                key = kmin; r = t;
+                token = nth_with_key(w, V, kmin, t, s_scan, &s_out);
             }
-            SLLM_TL(324);
-            token = nth_with_key(w, V, key, r, s_scan, &s_out);
             SLLM_TL(325);
             if (tid == 0 && (!a.seeded || kept >= 2)) a.st.draw_idx[slot] += 1;
         }
