@@ -50,21 +50,35 @@ struct FusedArgs {
     int upc;                                 // FFN: hidden units per block
 };
 
+// RMSNorm gains of the (up to two) elements a thread normalises; weights, so they can be fetched before the wait
+struct GainPf { float g[2]; };
+__device__ __forceinline__ GainPf gain_prefetch(const FusedArgs& a) {
+    GainPf p;
+    p.g[0] = threadIdx.x < a.m.D ? a.gain[threadIdx.x] : 0.f;
+    p.g[1] = threadIdx.x + kFusedThreads < a.m.D ? a.gain[threadIdx.x + kFusedThreads] : 0.f;
+    return p;
+}
+
 // x = x_in (+ partial sums), stored as the new residual by the designated block; xs = RMSNorm(x) * gain.
 // The 1 + n_parts source vectors are split into up to 3 groups of threads, each thread requests its group's
 // 16-byte pieces together (one round trip to L2 for up to 10 sources), the groups are combined in shared
-// memory in a fixed order.  `scratch` holds 2 * D floats.
-__device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, float* scratch, float* red, bool store) {
+// memory in a fixed order.  `scratch` holds 2 * D floats.  `after_issue` runs once the first batch of loads
+// is in flight and before its data is needed: the place for other loads that should overlap with it.
+template <typename F>
+__device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, float* scratch, float* red, bool store,
+                                               const GainPf& gp, F after_issue) {
     const int D = a.m.D, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* base = a.emb ? a.emb + (size_t)a.tok_id[0] * D : a.x_in;
     const int nch = D / 4;
     const int ng = max(1, min(3, kFusedThreads / nch));
     const int nsrc = 1 + a.n_parts_in, per = (nsrc + ng - 1) / ng;
-    for (int item = tid; item < ng * nch; item += kFusedThreads) {
-        const int g = item / nch, c = item - g * nch;
-        const int s_end = min(nsrc, (g + 1) * per);
+    bool called = false;
+    for (int item = tid; item < ng * nch || !called; item += kFusedThreads) {
+        const bool live = item < ng * nch;
+        const int g = live ? item / nch : 0, c = live ? item - g * nch : 0;
+        const int s_end = live ? min(nsrc, (g + 1) * per) : 0;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = g * per; s0 < s_end; s0 += 10) {
+        for (int s0 = g * per; s0 < s_end || !called; s0 += 10) {
             float4 t[10];
 #pragma unroll
             for (int i = 0; i < 10; ++i) {
@@ -72,10 +86,11 @@ __device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, fl
                 const float* src = sidx == 0 ? base : a.parts_in + (size_t)(sidx - 1) * D;
                 t[i] = sidx < s_end ? __ldcg(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            if (!called) { after_issue(); called = true; }
 #pragma unroll
             for (int i = 0; i < 10; ++i) { acc.x += t[i].x; acc.y += t[i].y; acc.z += t[i].z; acc.w += t[i].w; }
         }
-        *reinterpret_cast<float4*>((g == 0 ? xs : scratch + (size_t)(g - 1) * D) + c * 4) = acc;
+        if (live) *reinterpret_cast<float4*>((g == 0 ? xs : scratch + (size_t)(g - 1) * D) + c * 4) = acc;
     }
     __syncthreads();
     float ss = 0.f;
@@ -93,7 +108,7 @@ __device__ __forceinline__ void fused_prologue(const FusedArgs& a, float* xs, fl
 #pragma unroll
     for (int w = 0; w < kFusedWarps; ++w) s += red[w];
     const float inv = 1.0f / sqrtf(s / (float)D + a.m.eps);
-    for (int k = tid; k < D; k += kFusedThreads) xs[k] = xs[k] * inv * a.gain[k];
+    for (int k = tid, j = 0; k < D; k += kFusedThreads, ++j) xs[k] = xs[k] * inv * (j < 2 ? gp.g[j] : a.gain[k]);
     __syncthreads();
 }
 
@@ -187,21 +202,25 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_attn_block(const FusedArgs
         const int n = (warp + kFusedWarps * i) * KPI + rsub;
         if (n < NR) wo_pf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(n0 + n) * D + head * HD) + sub);
     }
+    const GainPf gp = gain_prefetch(a);
     cluster.sync();                            // every block of the head is running: its shared memory may be written
     SLLM_TL(101);
     pdl_wait();
     SLLM_TL(102);
 
     // ---- residual, norm, this block's rows of q, k, v ----------------------------------------------------
+    // position and slot are requested together with the residual; what depends on them (RoPE factors, the
+    // page of the new key, this block's first page) is requested as soon as they arrive, while the norm runs
     const int pos = a.tok_pos[0], slot = a.tok_slot[0];
-    // what depends only on the position is requested now and arrives while the norm runs
     float2 cs_first = make_float2(1.f, 0.f);
-    if (warp < NP && warp / (RP / 2) < 2)
-        cs_first = a.rope[(size_t)pos * (HD / 2) + ((c * RP + 2 * (warp % (RP / 2))) >> 1)];
-    const int n_pages = pos / kPage + 1;
-    const int page_new = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
-    const int page_first = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + min(c, n_pages - 1)];
-    fused_prologue(a, xs, xs + D, red, c == 0 && head == 0);
+    int n_pages = 1, page_new = 0, page_first = 0;
+    fused_prologue(a, xs, xs + D, red, c == 0 && head == 0, gp, [&]() {
+        if (warp < NP && warp / (RP / 2) < 2)
+            cs_first = a.rope[(size_t)pos * (HD / 2) + ((c * RP + 2 * (warp % (RP / 2))) >> 1)];
+        n_pages = pos / kPage + 1;
+        page_new = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
+        page_first = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + min(c, n_pages - 1)];
+    });
     SLLM_TL(103);
     for (int pi = warp; pi < NP; pi += kFusedWarps) {
         const int row = pair_row(pi);
@@ -415,11 +434,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         const int u = ug + G * i;
         if (ug < G && u < nu) dpf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
     }
+    const GainPf gp = gain_prefetch(a);
     SLLM_TL(201);
     pdl_wait();
     SLLM_TL(202);
 
-    fused_prologue(a, xs, s_y, red, blockIdx.x == 0);
+    fused_prologue(a, xs, s_y, red, blockIdx.x == 0, gp, []() {});
     SLLM_TL(203);
     // gate / up rows of this block's hidden units: silu(g) * u, src/nn/swiglu.cpp:37-57
     for (int u = warp; u < nu; u += kFusedWarps) {

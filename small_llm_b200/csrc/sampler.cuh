@@ -135,6 +135,7 @@ __device__ int scan_pick(unsigned long long my_m, unsigned int my_c, int top, Sa
     if (lane == 31) { s.sc_m[wp] = inc_m; s.sc_c[wp] = inc_c; }
     __syncthreads();
     unsigned long long off_m = 0; unsigned int off_c = 0;
+#pragma unroll 8
     for (int k = 0; k < wp; ++k) { off_m += s.sc_m[k]; off_c += s.sc_c[k]; }
     inc_m += off_m; inc_c += off_c;
     if (b >= 0 && my_c > 0 && cum + inc_m >= target) atomicMin(&s.pick, tid);
@@ -262,6 +263,7 @@ __device__ int cand_solve(const float* w, int V, uint32_t lo, uint32_t hi, unsig
     if (tid < n) {
         mk = cs.key[tid]; mi = cs.id[tid];
         int rank = 0;
+#pragma unroll 8
         for (int j = 0; j < n; ++j) {
             const uint32_t kj = cs.key[j];
             rank += (kj > mk) || (kj == mk && cs.id[j] < mi);
@@ -279,6 +281,7 @@ __device__ int cand_solve(const float* w, int V, uint32_t lo, uint32_t hi, unsig
     if (lane == 31) cs.warp_m[wp] = inc;
     __syncthreads();
     unsigned long long off = 0;
+#pragma unroll 8
     for (int k = 0; k < wp; ++k) off += cs.warp_m[k];
     inc += off;
     if (tid < n && inc >= need) atomicMin(&cs.pick, tid);
