@@ -22,6 +22,7 @@
 
 #include "../../include/sllm.h"
 #include "attn_decode.cuh"
+#include "attn_stream.cuh"
 #include "common.cuh"
 #include "decode_fused.cuh"
 #include "gemm_tc.cuh"
@@ -109,6 +110,7 @@ struct sllm_engine {
     // fused single-token decode path
     float* xb = nullptr; float* attn_parts = nullptr; float* down_parts = nullptr;
     std::vector<void*> wdT;                          // per layer: down weights as [F][D]
+    bool use_attn_stream = true;
     int fused_upc = 0, fused_nb = 0;
     bool fused_ok = false;
     // attention scratch
@@ -219,8 +221,22 @@ int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
     return launch_gemv_pf<WT, MODE, 3>(e, a, pdl, nt, grid, smem);
 }
 
+template <typename KVT, int HD>
+int launch_attn_stream_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
+    return launch(e, k_attn_stream<KVT, HD>, dim3(1, a.m.H, a.pass.n_tok), dim3(kStreamThreads), attn_stream_smem<KVT, HD>(), pdl, a,
+                  e->d_status);
+}
+
 template <typename KVT>
 int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
+    if (a.n_splits == 1 && e->use_attn_stream) {       // many (token, head) pairs: stream pages through shared memory
+        switch (a.m.hd) {
+            case 16: return launch_attn_stream_hd<KVT, 16>(e, a, pdl);
+            case 32: return launch_attn_stream_hd<KVT, 32>(e, a, pdl);
+            case 64: return launch_attn_stream_hd<KVT, 64>(e, a, pdl);
+            case 128: return launch_attn_stream_hd<KVT, 128>(e, a, pdl);
+        }
+    }
     const dim3 grid(a.n_splits, a.m.H, a.pass.n_tok), block(kAttnThreads);
     switch (a.m.hd) {
         case 16: return launch(e, k_attn_decode<KVT, 16>, grid, block, 0, pdl, a);
@@ -326,8 +342,9 @@ int pick_bn(const sllm_engine* e, int R, int n) {
     if (n <= 32) return 32;
     if (n <= 64) return 64;
     const int tiles_m = (R + kTcBM - 1) / kTcBM;
-    for (int bn : {256, 128}) if (tiles_m * ((n + bn - 1) / bn) >= e->sm_count) return bn;
-    return n <= 128 ? 128 : 64;
+    for (int bn : {256, 128, 64}) if (tiles_m * ((n + bn - 1) / bn) >= e->sm_count) return bn;
+    // few weight-row tiles (out / down projections): narrower token tiles put more SMs to work
+    return tiles_m * ((n + 63) / 64) * 2 <= e->sm_count ? 32 : 64;
 }
 
 template <int MODE>
@@ -498,7 +515,16 @@ int configure_gemv(sllm_engine* e) {
 }
 template <typename WT>
 int configure_kernels_t(sllm_engine* e) {
-    int rc = configure_gemv<WT, kModeQKV>(e);
+    auto big = [&](auto kern, size_t bytes) -> int {
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        return SLLM_OK;
+    };
+    int rc = big(k_attn_stream<WT, 16>, attn_stream_smem<WT, 16>());
+    if (!rc) rc = big(k_attn_stream<WT, 32>, attn_stream_smem<WT, 32>());
+    if (!rc) rc = big(k_attn_stream<WT, 64>, attn_stream_smem<WT, 64>());
+    if (!rc) rc = big(k_attn_stream<WT, 128>, attn_stream_smem<WT, 128>());
+    if (rc) return rc;
+    rc = configure_gemv<WT, kModeQKV>(e);
     if (!rc) rc = configure_gemv<WT, kModeResidual>(e);
     if (!rc) rc = configure_gemv<WT, kModeGateUp>(e);
     if (!rc) rc = configure_gemv<WT, kModeHead>(e);

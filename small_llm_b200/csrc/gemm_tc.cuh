@@ -101,7 +101,7 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
 
 template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
 template <int BN> __host__ __device__ constexpr size_t tc_smem_bytes() {
-    return 1024 + (size_t)tc_stages<BN>() * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + 256;
+    return 1024 + (size_t)tc_stages<BN>() * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + 256 + 4 * 2 * BN * sizeof(int);
 }
 
 template <int BN, int MODE>
@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     uint8_t* sB = smem + STAGES * A_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[S], empty[S], done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    int* tok_meta = reinterpret_cast<int*>(tmem_slot + 2);                  // [4 epilogue warps][pos[BN] | page[BN]]
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,49 +170,90 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     } else {
         // ---- epilogue: warps 2..5 own TMEM lane quarters 2,3,0,1 ---------------------------------------
         const int quarter = warp & 3;
-        ok = mbar_wait(done_bar, 0, a.status, 13);
-        ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
-        tc_fence_after();
         const int row = m0 + quarter * 32 + lane;
         const bool row_ok = row < a.R;
-        // per-row constants
         const int D = a.m.D, hd = a.m.hd;
         int which = 0, col = 0, head = 0, d = 0;
         if (MODE == kModeQKV && row_ok) { which = row / D; col = row - which * D; head = col / hd; d = col - head * hd; }
+        // While the tensor cores work, each epilogue warp fetches the positions and KV pages of the tile's
+        // tokens into its own shared-memory copy, so the epilogue below has no dependent global loads.
+        int* my_pos = tok_meta + (warp - 2) * 2 * BN;
+        int* my_page = my_pos + BN;
+        if (MODE == kModeQKV) {
+            for (int j = lane; j < BN; j += 32) {
+                const int tok = t0 + j;
+                int pos = 0, page = 0;
+                if (tok < a.n_tok) {
+                    pos = a.pass.tok_pos[tok];
+                    page = a.kv.block_table[(size_t)a.pass.tok_slot[tok] * a.kv.pages_per_seq + pos / kPage];
+                }
+                my_pos[j] = pos; my_page[j] = page;
+            }
+            __syncwarp();
+        }
+        ok = mbar_wait(done_bar, 0, a.status, 13);
+        ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
+        tc_fence_after();
         for (int c0 = 0; c0 < BN && ok; c0 += 32) {
             if (t0 + c0 >= a.n_tok) break;                       // uniform over the block
             uint32_t v[32];
             tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+            if (MODE == kModeResidual) {
+                // read-modify-write of the residual stream: 16 independent loads, then 16 stores
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int tok = t0 + c0 + j;
-                const float acc = __uint_as_float(v[j]);
-                // rows come in pairs (even lane, odd lane): a RoPE pair or a (gate, up) pair
-                const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
-                if (tok >= a.n_tok || !row_ok) continue;
-                if (MODE == kModeResidual) {
-                    float* x = a.out + (size_t)tok * a.R + row;
-                    *x = *x + acc;
-                } else if (MODE == kModeHead) {
-                    a.out[(size_t)tok * a.R + row] = acc;
-                } else if (MODE == kModeGateUp) {
-                    if ((row & 1) == 0) {
+                for (int jb = 0; jb < 32; jb += 16) {
+                    float xv[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = t0 + c0 + jb + j;
+                        xv[j] = (row_ok && tok < a.n_tok) ? a.out[(size_t)tok * a.R + row] : 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = t0 + c0 + jb + j;
+                        if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = xv[j] + __uint_as_float(v[jb + j]);
+                    }
+                }
+            } else if (MODE == kModeHead) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = t0 + c0 + j;
+                    if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = __uint_as_float(v[j]);
+                }
+            } else if (MODE == kModeGateUp) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = t0 + c0 + j;
+                    const float acc = __uint_as_float(v[j]);
+                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);      // (gate, up) sit in adjacent lanes
+                    if (row_ok && tok < a.n_tok && (row & 1) == 0) {
                         const float sig = 1.0f / (1.0f + expf(-acc));
                         a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn((acc * sig) * other);
                     }
-                } else {
-                    float o = acc;
-                    const int pos = a.pass.tok_pos[tok];
-                    if (which < 2) {
-                        const float2 cs = a.rope[(size_t)pos * (hd / 2) + (d >> 1)];
-                        o = (row & 1) ? (other * cs.y + acc * cs.x) : (acc * cs.x - other * cs.y);
-                    }
-                    if (which == 0) {
-                        a.out[(size_t)tok * D + col] = o;
-                    } else {
-                        const int slot = a.pass.tok_slot[tok];
-                        const int page = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
-                        kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, page, which - 1, head, pos % kPage)[d] = __float2bfloat16_rn(o);
+                }
+            } else {
+                // RoPE pairs sit in adjacent lanes; factors are fetched 8 tokens at a time
+#pragma unroll
+                for (int jb = 0; jb < 32; jb += 8) {
+                    float2 cs[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        cs[j] = (which < 2 && row_ok) ? a.rope[(size_t)my_pos[c0 + jb + j] * (hd / 2) + (d >> 1)] : make_float2(1.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int tok = t0 + c0 + jb + j;
+                        const float acc = __uint_as_float(v[jb + j]);
+                        const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                        if (!row_ok || tok >= a.n_tok) continue;
+                        float o = acc;
+                        if (which < 2) o = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
+                        if (which == 0) {
+                            a.out[(size_t)tok * D + col] = o;
+                        } else {
+                            const int pos = my_pos[c0 + jb + j];
+                            kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, my_page[c0 + jb + j], which - 1, head, pos % kPage)[d] =
+                                __float2bfloat16_rn(o);
+                        }
                     }
                 }
             }
