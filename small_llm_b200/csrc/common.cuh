@@ -93,11 +93,15 @@ struct ModelDims {
 };
 
 // Per-pass token list: token i of the pass belongs to slot tok_slot[i] at position tok_pos[i].
+struct PfTile { int tok_begin, n_q, slot, pos0; };   // pass tokens [tok_begin, tok_begin+n_q) of one slot at positions pos0..
+
 struct PassView {
     const uint32_t* tok_id;
     const int* tok_slot;
     const int* tok_pos;
     int n_tok;
+    const PfTile* tiles;      // prefill passes: runs of consecutive positions, <= 64 queries each (else null)
+    int n_tiles;
 };
 
 struct KvView {

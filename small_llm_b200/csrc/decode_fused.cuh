@@ -435,6 +435,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         if (ug < G && u < nu) dpf[i] = ldg_stream(reinterpret_cast<const uint4*>(W2 + (size_t)(j0 + u) * D) + ch);
     }
     const GainPf gp = gain_prefetch(a);
+    cluster.sync();                              // all 8 blocks are running: their shared memory may be written later
     SLLM_TL(201);
     pdl_wait();
     SLLM_TL(202);
@@ -473,27 +474,25 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
         for (int e = 0; e < EPC; ++e) s_y[(size_t)ug * D + ch * EPC + e] = acc[e];
     }
     __syncthreads();
+    // every block hands each column to the block of its cluster that owns it (columns [r*D/8, (r+1)*D/8) belong
+    // to rank r), one barrier, then the owner adds the 8 contributions from its own shared memory in rank order
+    const int NR = D / kCS;
+    float* rx = s_y + (size_t)max(G, 2) * D;     // [kCS][NR], written by the peers
     for (int n = tid; n < D; n += kFusedThreads) {
-        float s = s_y[n];
-        for (int g = 1; g < G; ++g) s += s_y[(size_t)g * D + n];
-        s_y[n] = s;
+        float v = s_y[n];
+        for (int g = 1; g < G; ++g) v += s_y[(size_t)g * D + n];
+        const int owner = n / NR;
+        cluster.map_shared_rank(rx, owner)[c * NR + (n - owner * NR)] = v;
     }
     SLLM_TL(205);
     cluster.sync();
     SLLM_TL(206);
-    // block c of the cluster adds up columns [c*D/8, (c+1)*D/8) of the 8 blocks, in rank order
-    const int NR = D / kCS;
     for (int n = tid; n < NR; n += kFusedThreads) {
-        float t[kCS];
+        float v = 0.f;
 #pragma unroll
-        for (int r = 0; r < kCS; ++r) t[r] = cluster.map_shared_rank(s_y, r)[c * NR + n];     // 8 loads in flight
-        float s = 0.f;
-#pragma unroll
-        for (int r = 0; r < kCS; ++r) s += t[r];
-        a.parts_out[(size_t)(blockIdx.x / kCS) * D + c * NR + n] = s;
+        for (int r = 0; r < kCS; ++r) v += rx[r * NR + n];
+        a.parts_out[(size_t)(blockIdx.x / kCS) * D + c * NR + n] = v;
     }
-    SLLM_TL(207);
-    cluster.sync();                              // peers may still be reading this block's shared memory
     SLLM_TL(208);
 }
 

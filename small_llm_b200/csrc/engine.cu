@@ -22,6 +22,7 @@
 
 #include "../../include/sllm.h"
 #include "attn_decode.cuh"
+#include "attn_prefill.cuh"
 #include "attn_stream.cuh"
 #include "common.cuh"
 #include "decode_fused.cuh"
@@ -96,6 +97,7 @@ struct sllm_engine {
     uint32_t* d_dec_id = nullptr; int* d_dec_slot = nullptr; int* d_dec_pos = nullptr;   // decode pass (written by the sampler)
     float* x = nullptr; float* q = nullptr; float* att = nullptr; float* hid = nullptr;
     int* d_row_tok = nullptr;
+    PfTile* d_tiles = nullptr;
     float* step_logits = nullptr;      // [max_batch][V]
     float* pass_logits = nullptr;      // [logit_rows_cap][V]
     int logit_rows_cap = 0;
@@ -227,8 +229,24 @@ int launch_attn_stream_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
                   e->d_status);
 }
 
+template <typename KVT, int HD>
+int launch_attn_prefill_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
+    AttnPfArgs p{};
+    p.q = a.q; p.out = a.out; p.out_bf16 = a.out_bf16; p.m = a.m; p.kv = a.kv; p.tiles = a.pass.tiles; p.layer = a.layer;
+    p.status = e->d_status;
+    return launch(e, k_attn_prefill<KVT, HD>, dim3(a.pass.n_tiles, a.m.H), dim3(kPfThreads), attn_prefill_smem<KVT, HD>(), pdl, p);
+}
+
 template <typename KVT>
 int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
+    if (a.pass.n_tiles > 0 && a.pass.n_tiles * 4 <= a.pass.n_tok) {      // long runs of one sequence: query tiles share the pages
+        switch (a.m.hd) {
+            case 16: return launch_attn_prefill_hd<KVT, 16>(e, a, pdl);
+            case 32: return launch_attn_prefill_hd<KVT, 32>(e, a, pdl);
+            case 64: return launch_attn_prefill_hd<KVT, 64>(e, a, pdl);
+            case 128: return launch_attn_prefill_hd<KVT, 128>(e, a, pdl);
+        }
+    }
     if (a.n_splits == 1 && e->use_attn_stream) {       // many (token, head) pairs: stream pages through shared memory
         switch (a.m.hd) {
             case 16: return launch_attn_stream_hd<KVT, 16>(e, a, pdl);
@@ -256,7 +274,7 @@ int run_pass_t(sllm_engine* e, const PassView& pv, const int* row_tok, int n_row
     const int n = pv.n_tok;
     // attention split policy: fill the GPU when few (token, head) pairs exist
     int n_splits = 1, kps = ((m.ctx + kPage - 1) / kPage) * kPage;
-    if (n <= e->split_tok_cap && n * m.H < 2 * e->sm_count) {
+    if (pv.n_tiles == 0 && n <= e->split_tok_cap && n * m.H < 2 * e->sm_count) {
         n_splits = std::min({kMaxSplits, e->pages_per_seq, std::max(1, 4 * e->sm_count / (n * m.H))});
         const int pages_per_split = (e->pages_per_seq + n_splits - 1) / n_splits;
         kps = pages_per_split * kPage;
@@ -342,9 +360,10 @@ int pick_bn(const sllm_engine* e, int R, int n) {
     if (n <= 32) return 32;
     if (n <= 64) return 64;
     const int tiles_m = (R + kTcBM - 1) / kTcBM;
-    for (int bn : {256, 128, 64}) if (tiles_m * ((n + bn - 1) / bn) >= e->sm_count) return bn;
-    // few weight-row tiles (out / down projections): narrower token tiles put more SMs to work
-    return tiles_m * ((n + 63) / 64) * 2 <= e->sm_count ? 32 : 64;
+    // the widest token tile that still gives at least half an SM count of blocks: wide tiles re-read the
+    // weight tile less often (shared-memory fill traffic from L2 is what bounds these small-K products)
+    for (int bn : {256, 128, 64}) if (tiles_m * ((n + bn - 1) / bn) * 2 >= e->sm_count) return bn;
+    return 32;
 }
 
 template <int MODE>
@@ -460,7 +479,7 @@ int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logi
     const ModelDims& m = e->md;
     const int chunks_per_lane = (m.D / Elems<WT>::per16 + 31) / 32;
     const int G = kFusedThreads / (m.D / Elems<WT>::per16);
-    const size_t smem_b = (size_t)(1 + std::max(G, 2)) * m.D * sizeof(float);
+    const size_t smem_b = (size_t)(2 + std::max(G, 2)) * m.D * sizeof(float);      // xs | group sums | receive buffer
     const int ncl = e->fused_nb / kCS;
     FusedArgs a{};
     a.m = m; a.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
@@ -519,7 +538,11 @@ int configure_kernels_t(sllm_engine* e) {
         CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
         return SLLM_OK;
     };
-    int rc = big(k_attn_stream<WT, 16>, attn_stream_smem<WT, 16>());
+    int rc = big(k_attn_prefill<WT, 16>, attn_prefill_smem<WT, 16>());
+    if (!rc) rc = big(k_attn_prefill<WT, 32>, attn_prefill_smem<WT, 32>());
+    if (!rc) rc = big(k_attn_prefill<WT, 64>, attn_prefill_smem<WT, 64>());
+    if (!rc) rc = big(k_attn_prefill<WT, 128>, attn_prefill_smem<WT, 128>());
+    if (!rc) rc = big(k_attn_stream<WT, 16>, attn_stream_smem<WT, 16>());
     if (!rc) rc = big(k_attn_stream<WT, 32>, attn_stream_smem<WT, 32>());
     if (!rc) rc = big(k_attn_stream<WT, 64>, attn_stream_smem<WT, 64>());
     if (!rc) rc = big(k_attn_stream<WT, 128>, attn_stream_smem<WT, 128>());
@@ -615,7 +638,7 @@ int grow_for_step(sllm_engine* e) {
     return SLLM_OK;
 }
 
-PassView decode_view(sllm_engine* e) { return PassView{e->d_dec_id, e->d_dec_slot, e->d_dec_pos, e->n_live}; }
+PassView decode_view(sllm_engine* e) { return PassView{e->d_dec_id, e->d_dec_slot, e->d_dec_pos, e->n_live, nullptr, 0}; }
 
 // One decode iteration = sampler, then the model over the sampled tokens.
 int enqueue_iteration(sllm_engine* e, const SampleArgs& s) {
@@ -829,6 +852,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
                  const int* slot_ids = nullptr) {
     const ModelDims& m = e->md;
     std::vector<uint32_t> c_id; std::vector<int> c_slot, c_pos, c_row; std::vector<int> c_row_dst;
+    std::vector<PfTile> c_tiles;
     c_id.reserve(e->pass_cap); c_slot.reserve(e->pass_cap); c_pos.reserve(e->pass_cap);
     size_t off = 0, row_base = 0;
     auto flush = [&]() -> int {
@@ -837,7 +861,8 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         CU(cudaMemcpyAsync(e->d_tok_id, c_id.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         CU(cudaMemcpyAsync(e->d_tok_slot, c_slot.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         CU(cudaMemcpyAsync(e->d_tok_pos, c_pos.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
-        PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n};
+        CU(cudaMemcpyAsync(e->d_tiles, c_tiles.data(), c_tiles.size() * sizeof(PfTile), cudaMemcpyHostToDevice, e->stream));
+        PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n, e->d_tiles, (int)c_tiles.size()};
         int rc = run_pass(e, pv, nullptr, 0, nullptr, false);
         if (rc) return rc;
         // logits rows of this chunk, in groups that fit the logits buffer
@@ -857,7 +882,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
             CU(cudaStreamSynchronize(e->stream));
         }
         row_base += c_row.size();
-        c_id.clear(); c_slot.clear(); c_pos.clear(); c_row.clear(); c_row_dst.clear();
+        c_id.clear(); c_slot.clear(); c_pos.clear(); c_row.clear(); c_row_dst.clear(); c_tiles.clear();
         return SLLM_OK;
     };
     for (uint32_t s = 0; s < n_seq; ++s) {
@@ -865,6 +890,11 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
             if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
             const int slot = slot_ids ? slot_ids[s] : (int)s;
             if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
+            if (!c_tiles.empty() && c_tiles.back().slot == slot && c_tiles.back().n_q < kPfQ &&
+                c_tiles.back().pos0 + c_tiles.back().n_q == (int)i && c_tiles.back().tok_begin + c_tiles.back().n_q == (int)c_id.size())
+                c_tiles.back().n_q += 1;
+            else
+                c_tiles.push_back(PfTile{(int)c_id.size(), 1, slot, (int)i});
             c_id.push_back(ids[off + i]); c_slot.push_back(slot); c_pos.push_back((int)i);
         }
         off += lens[s];
@@ -1030,6 +1060,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->d_dec_id, e->max_batch, &e->scratch_bytes); A(&e->d_dec_slot, e->max_batch, &e->scratch_bytes);
     A(&e->d_dec_pos, e->max_batch, &e->scratch_bytes);
     A(&e->d_row_tok, e->pass_cap, &e->scratch_bytes);
+    A(&e->d_tiles, e->pass_cap, &e->scratch_bytes);
     A(&e->x, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->q, (size_t)e->pass_cap * D, &e->scratch_bytes);
     A(&e->att, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->hid, (size_t)e->pass_cap * F, &e->scratch_bytes);
     A(&e->step_logits, (size_t)e->max_batch * V, &e->scratch_bytes);
@@ -1040,7 +1071,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
         e->fused_upc = std::max<int>((int)((F + 143) / 144), 2);
         e->fused_nb = (int)(((F + e->fused_upc - 1) / e->fused_upc + kCS - 1) / kCS) * kCS;
         e->fused_ok = nch <= kFusedThreads && e->fused_upc <= 64 && D % kCS == 0 &&
-                      (size_t)(1 + std::max(kFusedThreads / nch, 2)) * D * sizeof(float) <= 48 * 1024;
+                      (size_t)(2 + std::max(kFusedThreads / nch, 2)) * D * sizeof(float) <= 48 * 1024;
         if (e->fused_ok) {
             A(&e->xb, D, &e->scratch_bytes);
             A(&e->attn_parts, H * D, &e->scratch_bytes);
@@ -1460,7 +1491,7 @@ int attn_decode_launch(sllm_engine* e, uint32_t layer, uint32_t n_tok, const flo
     AttnDecArgs t{};
     t.q = d_q; t.out = d_out; t.out_bf16 = nullptr; t.m = m;
     t.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
-    t.pass = PassView{nullptr, d_slot, d_pos, (int)n_tok};
+    t.pass = PassView{nullptr, d_slot, d_pos, (int)n_tok, nullptr, 0};
     t.layer = (int)layer;
     const int pages_per_split = (e->pages_per_seq + (int)n_splits - 1) / (int)n_splits;
     t.keys_per_split = pages_per_split * kPage;
