@@ -496,6 +496,22 @@ __global__ void __launch_bounds__(kFusedThreads, 2) k_ffn_block(const FusedArgs 
     SLLM_TL(208);
 }
 
+// Final RMSNorm of the single-token path, once: xn = RMSNorm(base + sum of partials) * gain.  The head kernel
+// then starts from 2.5 KB instead of every one of its blocks re-reading 19 vectors.
+__global__ void __launch_bounds__(kFusedThreads) k_final_norm(const float* __restrict__ base, const float* __restrict__ parts,
+                                                              int n_parts, int D, const float* __restrict__ gain, float eps,
+                                                              float* __restrict__ xn) {
+    extern __shared__ __align__(16) float fx[];          // [3 * D]
+    __shared__ float red[kFusedWarps];
+    FusedArgs a{};
+    a.m.D = D; a.m.eps = eps; a.x_in = base; a.parts_in = parts; a.n_parts_in = n_parts; a.gain = gain;
+    pdl_launch_dependents();
+    const GainPf gp = gain_prefetch(a);
+    pdl_wait();
+    fused_prologue(a, fx, fx + D, red, false, gp, []() {});
+    for (int k = threadIdx.x; k < D; k += kFusedThreads) xn[k] = fx[k];
+}
+
 // x[k] = base[k] + sum of partials, for callers that want the finished residual stream in one buffer
 __global__ void __launch_bounds__(256) k_sum_parts(const float* __restrict__ base, const float* __restrict__ parts, int n_parts,
                                                    int D, float* __restrict__ out) {

@@ -211,7 +211,7 @@ int launch_gemv_pf(sllm_engine* e, const GemvArgs& a, bool pdl, int nt, dim3 gri
 template <typename WT, int MODE>
 int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
     const int groups = a.R / 2;
-    int gx = std::min((groups + kGemvWarps - 1) / kGemvWarps, e->sm_count * 4);
+    int gx = std::min((groups + kGemvWarps - 1) / kGemvWarps, e->sm_count * (a.prenorm ? 16 : 4));
     const int n = a.n_tok;
     int nt = n == 1 ? 1 : (n == 2 ? 2 : (n <= 4 ? 4 : 8));
     const size_t smem = (size_t)nt * a.K * sizeof(float);
@@ -500,9 +500,12 @@ int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logi
         if (rc) return rc;
     }
     if (n_rows > 0) {
+        int rc = launch(e, k_final_norm, dim3(1), dim3(kFusedThreads), (size_t)3 * m.D * sizeof(float), pdl, (const float*)e->xb,
+                        (const float*)e->down_parts, ncl, m.D, (const float*)e->g_final, m.eps, e->q);
+        if (rc) return rc;
         GemvArgs h{};
-        h.m = m; h.eps = m.eps; h.W = e->emb_w; h.R = m.V; h.K = m.D; h.in = e->xb; h.gain = e->g_final;
-        h.parts = e->down_parts; h.n_parts = ncl; h.out = logits; h.n_tok = 1; h.pass = pv;
+        h.m = m; h.eps = m.eps; h.W = e->emb_w; h.R = m.V; h.K = m.D; h.in = e->q; h.gain = e->g_final; h.prenorm = 1;
+        h.out = logits; h.n_tok = 1; h.pass = pv;
         return launch_gemv<WT, kModeHead>(e, h, pdl);
     }
     // no logits wanted: leave the finished residual in e->x, where the other paths keep it

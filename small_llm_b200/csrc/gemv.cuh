@@ -37,6 +37,7 @@ struct GemvArgs {
     const float2* rope;       // [ctx][hd/2] (cos, sin)
     const float* parts;       // single-token passes: [n_parts][K] partial sums that complete the residual `in`
     int n_parts;
+    int prenorm;              // Head: `in` already holds the normalised vector (k_final_norm): no norm here
     const float* emb;         // layer 0: fp32 embedding table [V][D]; x is gathered from it ...
     float* x_out;             // ... and written here by block column 0
     float eps;
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(kGemvThreads) k_gemv(const GemvArgs a) {
     const int K = a.K;
     const int t0 = blockIdx.y * NT;
     const int nt = min(NT, a.n_tok - t0);
-    constexpr bool kNorm = (MODE != kModeResidual);
+    const bool kNorm = (MODE != kModeResidual) && !(MODE == kModeHead && a.prenorm);
 
     // ---- weights of this warp's first row pair: in flight before anything else -------------------
     const int nchunk = K / EPC;
