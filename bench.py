@@ -206,18 +206,24 @@ def run_ours(args):
             "metric": "decode tok/s at batch 1 (1 B200) vs HBM roofline; p50 per-token ms",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": ms / args.steps, "per_token_ms": step_ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 weights+KV, f32 accumulate",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: N(0,0.02) weights (numpy seed 0), std::mt19937 prompt ids and draws",
             "config": {"workload": "BASELINE config 2: 100.3M model, batch 1 per GPU, prompt 256, 512 sampled decode steps "
                                    "(T 0.8, top-p 0.95, penalty 1.15, host draws)",
-                       "sequences_per_gpu": 1, "l2": "inputs larger than L2 (200.6 MB of weights streamed per token)"},
+                       "sequences_per_gpu": 1, "precision": "bf16 weights and KV cache, fp32 residual stream and accumulation",
+                       "l2": "inputs larger than L2 (200.6 MB of weights streamed per token)"},
             "e2e": {"value": world * N_NEW / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(N_PROMPT * 4 + N_NEW * 8), "d2h_bytes_per_step": int((N_PROMPT + N_NEW + 1) * 4),
                     "note": "sllm_generate with host buffers: prompt upload, prefill of 256 ids, 512 decode steps, token download"},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "one decode step = CUDA graph of sampler + 16 x (qkv, attention, out, gate/up, down) + head",
+            "roofline": {"bound": "hbm",
+                         "kernel": "one decode step = one CUDA-graph replay: 3 sampler kernels + 16 x (k_attn_block, k_ffn_block) + final norm + head",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "algorithmic_bytes_per_token": bytes_tok, "traffic": None},
+                         "peak_kind": peak_kind + " copy bandwidth (burst figure; the step is latency-bound)",
+                         "algorithmic_bytes_per_token": bytes_tok,
+                         # dram__bytes_read+write summed over the kernels of one step, ncu capture at context 260
+                         # (profiles/decode_step_batch1_launch_list.md): the weights; KV pages were served by L2
+                         "traffic": 200.3e6},
             "clocks": clocks.summary(),
         }
         if args.profile_only:
