@@ -35,6 +35,9 @@ if ROOT not in sys.path:
 N_PROMPT, N_NEW = 256, 512
 SAMPLING = dict(temperature=0.8, top_p=0.95, repetition_penalty=1.15)
 EOS_NEVER = 1 << 30            # a sequence must run its full 512 steps to be comparable
+METRIC = "decode tok/s at batch 1 (1 B200) vs HBM roofline; p50 per-token ms"
+WORKLOAD = ("BASELINE config 2: 100.3M model, batch 1 per GPU, prompt 256, 512 sampled decode steps "
+            "(T 0.8, top-p 0.95, penalty 1.15, host draws)")
 
 
 def mt19937_raw(seed: int, n: int) -> np.ndarray:
@@ -203,13 +206,12 @@ def run_ours(args):
         bytes_tok = algorithmic_bytes_per_token(cfg, ctx_mean)
         achieved = bytes_tok / (step_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode tok/s at batch 1 (1 B200) vs HBM roofline; p50 per-token ms",
+            "metric": METRIC,
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": ms / args.steps, "per_token_ms": step_ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: N(0,0.02) weights (numpy seed 0), std::mt19937 prompt ids and draws",
-            "config": {"workload": "BASELINE config 2: 100.3M model, batch 1 per GPU, prompt 256, 512 sampled decode steps "
-                                   "(T 0.8, top-p 0.95, penalty 1.15, host draws)",
+            "config": {"workload": WORKLOAD,
                        "sequences_per_gpu": 1, "precision": "bf16 weights and KV cache, fp32 residual stream and accumulation",
                        "l2": "inputs larger than L2 (200.6 MB of weights streamed per token)"},
             "e2e": {"value": world * N_NEW / (e2e_ms * 1e-3), "unit": "tokens/s",
@@ -381,12 +383,11 @@ def run_reference(args):
     sample = (f"each step = one token of the reference's own loop on CPU (full forward over a {window}-id window, no KV "
               f"cache, + host sampler); configured window {N_PROMPT}..{N_PROMPT + N_NEW - 1}, cost linear in the window")
     print(json.dumps({
-        "impl": "reference", "metric": "decode tok/s at batch 1 (1 B200) vs HBM roofline; p50 per-token ms",
+        "impl": "reference", "metric": METRIC,
         "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic: N(0,0.02) weights (reference generator, seed 0), std::mt19937 prompt ids",
-        "config": {"workload": "BASELINE config 2: 100.3M model, batch 1, prompt 256, 512 sampled decode steps "
-                               "(T 0.8, top-p 0.95, penalty 1.15)"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
