@@ -65,8 +65,9 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     __shared__ float red_l[KG];
     __shared__ float s_q[HD];
     __shared__ int s_ok;
+    __shared__ unsigned int s_last;
 
-    const int head = blockIdx.y, tok = blockIdx.z;
+    const int split = blockIdx.x, head = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (tid == 0) {
@@ -80,8 +81,12 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     const int pos = a.pass.tok_pos[tok];
     const int slot = a.pass.tok_slot[tok];
     const int D = a.m.D;
-    const int n_pages = pos / kPage + 1;
-    const int* table = a.kv.block_table + (size_t)slot * a.kv.pages_per_seq;
+    const int all_pages = pos / kPage + 1;
+    // with several splits each block takes an equal share of the pages this query actually has
+    const int per_split = (all_pages + a.n_splits - 1) / a.n_splits;
+    const int pg0 = split * per_split;
+    const int n_pages = max(0, min(all_pages, pg0 + per_split) - pg0);
+    const int* table = a.kv.block_table + (size_t)slot * a.kv.pages_per_seq + pg0;
     if (tid < HD) s_q[tid] = a.q[(size_t)tok * D + head * HD + tid];
     __syncthreads();
 
@@ -110,7 +115,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         if (!s_ok) break;                         // uniform after the barrier
         const KVT* Kp = reinterpret_cast<const KVT*>(smem_raw + (size_t)s * 2 * BLK);
         const KVT* Vp = reinterpret_cast<const KVT*>(smem_raw + (size_t)s * 2 * BLK + BLK);
-        const int nk = min(kPage, pos + 1 - pg * kPage);
+        const int nk = min(kPage, pos + 1 - (pg0 + pg) * kPage);
         for (int j = warp * KPI + lane / LPK; j < kPage; j += WARPS * KPI) {
             float sdot = 0.f;
             if (j < nk) {
@@ -155,14 +160,46 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     red_o[kg][2 * dp + 1] = o1;
     if (dp == 0) red_l[kg] = l_run;
     __syncthreads();
+    float o = 0.f, l = 0.f;
     if (tid < HD) {
-        float o = 0.f, l = 0.f;
 #pragma unroll
         for (int g = 0; g < KG; ++g) { o += red_o[g][tid]; l += red_l[g]; }
-        const float r = o / l;
+    }
+    if (a.n_splits == 1) {
+        if (tid < HD) {
+            const float r = o / l;
+            a.out[(size_t)tok * D + head * HD + tid] = r;
+            if (a.out_bf16) a.out_bf16[(size_t)tok * D + head * HD + tid] = __float2bfloat16_rn(r);
+        }
+        return;
+    }
+    // several splits: publish the partial; the block that takes the last ticket merges in split order
+    const size_t pidx = ((size_t)tok * a.m.H + head) * a.n_splits + split;
+    if (tid < HD) a.part_o[pidx * HD + tid] = o;
+    if (tid == 0) { a.part_ml[pidx * 2] = m_run; a.part_ml[pidx * 2 + 1] = l; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&a.ticket[(size_t)tok * a.m.H + head], 1u) == (unsigned int)a.n_splits - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const size_t base = ((size_t)tok * a.m.H + head) * a.n_splits;
+    float mx = -INFINITY;
+    for (int sp = 0; sp < a.n_splits; ++sp) mx = fmaxf(mx, __ldcg(a.part_ml + (base + sp) * 2));
+    if (tid < HD) {
+        float num = 0.f, den = 0.f;
+        for (int sp = 0; sp < a.n_splits; ++sp) {
+            const float ms = __ldcg(a.part_ml + (base + sp) * 2);
+            if (ms == -INFINITY) continue;
+            const float w = expf(ms - mx);
+            den += w * __ldcg(a.part_ml + (base + sp) * 2 + 1);
+            num += w * __ldcg(a.part_o + (base + sp) * HD + tid);
+        }
+        const float r = num / den;
         a.out[(size_t)tok * D + head * HD + tid] = r;
         if (a.out_bf16) a.out_bf16[(size_t)tok * D + head * HD + tid] = __float2bfloat16_rn(r);
     }
+    if (tid == 0) a.ticket[(size_t)tok * a.m.H + head] = 0;
 }
 
 template <typename KVT, int HD> constexpr size_t attn_stream_smem() {

@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <random>
@@ -225,8 +226,8 @@ int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
 
 template <typename KVT, int HD>
 int launch_attn_stream_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
-    return launch(e, k_attn_stream<KVT, HD>, dim3(1, a.m.H, a.pass.n_tok), dim3(kStreamThreads), attn_stream_smem<KVT, HD>(), pdl, a,
-                  e->d_status);
+    return launch(e, k_attn_stream<KVT, HD>, dim3(a.n_splits, a.m.H, a.pass.n_tok), dim3(kStreamThreads), attn_stream_smem<KVT, HD>(),
+                  pdl, a, e->d_status);
 }
 
 template <typename KVT, int HD>
@@ -247,7 +248,7 @@ int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
             case 128: return launch_attn_prefill_hd<KVT, 128>(e, a, pdl);
         }
     }
-    if (a.n_splits == 1 && e->use_attn_stream) {       // many (token, head) pairs: stream pages through shared memory
+    if ((a.n_splits == 1 || a.pass.n_tok * a.m.H >= e->sm_count) && e->use_attn_stream) {   // stream pages through shared memory
         switch (a.m.hd) {
             case 16: return launch_attn_stream_hd<KVT, 16>(e, a, pdl);
             case 32: return launch_attn_stream_hd<KVT, 32>(e, a, pdl);
@@ -357,9 +358,9 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, c
 
 // token-tile width: wide tiles for arithmetic intensity, narrower ones while the grid would not fill the GPU
 int pick_bn(const sllm_engine* e, int R, int n) {
-    if (n <= 32) return 32;
-    if (n <= 64) return 64;
     const int tiles_m = (R + kTcBM - 1) / kTcBM;
+    if (n <= 32) return 32;
+    if (n <= 64) return tiles_m * 2 <= e->sm_count ? 32 : 64;      // small projections: two token tiles, twice the blocks
     // the widest token tile that still gives at least half an SM count of blocks: wide tiles re-read the
     // weight tile less often (shared-memory fill traffic from L2 is what bounds these small-K products)
     for (int bn : {256, 128, 64}) if (tiles_m * ((n + bn - 1) / bn) * 2 >= e->sm_count) return bn;
@@ -414,7 +415,9 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
         if (rc) return rc;
         AttnDecArgs t{};
         t.q = e->q; t.out = e->att; t.out_bf16 = e->att16; t.m = m; t.kv = kv; t.pass = pv; t.layer = l;
-        t.n_splits = 1; t.keys_per_split = e->pages_per_seq * kPage;
+        // few (token, head) pairs: split each one's pages over up to 4 blocks so that every SM has ~8 blocks
+        t.n_splits = (pv.n_tiles == 0 && n <= e->split_tok_cap) ? std::max(1, std::min(4, (8 * e->sm_count) / (n * m.H))) : 1;
+        t.keys_per_split = e->pages_per_seq * kPage;
         t.part_o = e->part_o; t.part_ml = e->part_ml; t.ticket = e->ticket;
         rc = launch_attn_any(e, t, pdl);
         if (rc) return rc;
@@ -972,6 +975,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     e->max_batch = (int)opt.max_batch;
     e->pages_per_seq = (m.ctx + kPage - 1) / kPage;
     e->n_pages = opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq;
+    if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);
     e->logit_rows_cap = std::max(e->max_batch, 64);

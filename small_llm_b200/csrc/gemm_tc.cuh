@@ -136,18 +136,29 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    pdl_wait();
     pdl_launch_dependents();
+    // The weight tiles do not depend on the predecessor kernel: the first STAGES of them are requested before
+    // the dependency wait (the barrier already expects the bytes of both operands of its stage).
+    const int pre = nkb < STAGES ? nkb : STAGES;
+    if (warp == 0 && lane == 0) {
+        for (int kb = 0; kb < pre; ++kb) {
+            mbar_expect_tx(full0 + 8 * kb, A_BYTES + B_BYTES);
+            tma_load_2d(smem_u32(sA + kb * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * kb);
+        }
+    }
+    pdl_wait();
 
     bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % STAGES;
-                if (kb >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, a.status, 11);
-                if (!ok) break;
-                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
-                tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * s);
+                if (kb >= pre) {
+                    ok = mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, a.status, 11);
+                    if (!ok) break;
+                    mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                    tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * s);
+                }
                 tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, kb * kTcBK, t0, full0 + 8 * s);
             }
         }
