@@ -150,6 +150,18 @@ int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* pr
  * the stream is idle.  draws_dev_index selects how draws are consumed as in sllm_generate. */
 int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws);
 
+/* ---- single slots: continuous batching ------------------------------------------------------
+ * No counterpart in the reference (it generates one sequence at a time); these keep a batched decode
+ * loop full: when a slot stops (EOS, stop token, budget), the caller collects its tokens, releases it
+ * and assigns the next prompt to it while the other slots keep their state. */
+/* Put a prompt (1..context_length ids) into one slot and run it through the model; other slots are untouched.
+ * Slots below `slot` that were never assigned are parked (idle). */
+int sllm_slot_assign(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_t len);
+/* Park a slot: its KV pages return to the pool, the sampler skips it. */
+int sllm_slot_release(sllm_engine* e, uint32_t slot);
+/* Finished flags of slots 0..n-1 to HOST memory: 0 live, 1 EOS / stop token / parked, 2 context full, 3 non-finite logits. */
+int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n);
+
 /* ---- single kernels, device pointers in and out --------------------------------------- */
 /* The flash-decode attention kernel on its own (the fused form of ops::attention for one cached
  * query position per token, src/ops/attention.cpp:143-184): d_q [n_tok][d_model] fp32 rotated

@@ -68,6 +68,7 @@ ABI_SYMBOLS = [
     "sllm_param_info", "sllm_set_param", "sllm_load_checkpoint", "sllm_forward_logits", "sllm_reset",
     "sllm_prefill", "sllm_sample", "sllm_decode_step", "sllm_get_step_logits", "sllm_get_tokens",
     "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
+    "sllm_slot_assign", "sllm_slot_release", "sllm_get_finished",
 ]
 
 
@@ -111,6 +112,9 @@ def load_library(path: str | None = None):
                                   C.c_uint64, u64p]
     lib.sllm_decode_loop.argtypes = [E, C.c_uint64, C.POINTER(_Sampling), f64p]
     i32p = C.POINTER(C.c_int32)
+    lib.sllm_slot_assign.argtypes = [E, C.c_uint32, u32p, C.c_uint32]
+    lib.sllm_slot_release.argtypes = [E, C.c_uint32]
+    lib.sllm_get_finished.argtypes = [E, i32p, C.c_uint32]
     for fn in (lib.sllm_k_attn_decode, lib.sllm_k_attn_decode_static):
         fn.argtypes = [E, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     if path is None:
@@ -309,6 +313,18 @@ class Engine:
                                         C.byref(s), dp, out.ctypes.data_as(u32p), stride,
                                         out_lens.ctypes.data_as(u64p)))
         return [out[i, : int(out_lens[i])].copy() for i in range(n)]
+
+    def slot_assign(self, slot: int, ids):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        self._ck(self.lib.sllm_slot_assign(self.h, slot, ids.ctypes.data_as(u32p), ids.size))
+
+    def slot_release(self, slot: int):
+        self._ck(self.lib.sllm_slot_release(self.h, slot))
+
+    def finished(self, n: int) -> np.ndarray:
+        out = np.zeros(n, dtype=np.int32)
+        self._ck(self.lib.sllm_get_finished(self.h, out.ctypes.data_as(C.POINTER(C.c_int32)), n))
+        return out
 
     def k_attn_decode(self, layer: int, n_tok: int, d_q: int, d_tok_slot: int, d_tok_pos: int, n_splits: int,
                       d_out: int, stream: int = 0, static_scratch: bool = False):

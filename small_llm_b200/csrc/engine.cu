@@ -91,6 +91,8 @@ struct sllm_engine {
     int max_batch = 0;
     int n_live = 0;                    // slots 0..n_live-1 are in use
     std::vector<int> h_len_bound;      // upper bound of each slot's token count (host view)
+    std::vector<char> slot_released;   // slot holds no sequence: its block table points at the spare page
+    int spare_page = 0;                // never handed out: idle slots write their (ignored) K/V there
 
     // pass buffers
     int pass_cap = 0;                  // tokens per pass
@@ -635,6 +637,7 @@ int launch_sampler(sllm_engine* e, const SampleArgs& s, bool pdl) {
 // host bound on lengths: one more token per live slot per sampling step
 int grow_for_step(sllm_engine* e) {
     for (int s = 0; s < e->n_live; ++s) {
+        if (e->slot_released[s]) continue;
         bool changed = false;
         e->h_len_bound[s] = std::min(e->h_len_bound[s] + 1, e->md.ctx + 1);
         int rc = ensure_pages(e, s, e->h_len_bound[s], &changed);
@@ -792,7 +795,7 @@ int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32
     }
     for (size_t i = 0; i < total; ++i)
         if (ids[i] >= (uint32_t)m.V) return fail(e, SLLM_ERR_INVALID, "token id outside the vocabulary");
-    for (int s = 0; s < e->max_batch; ++s) release_slot(e, s);
+    for (int s = 0; s < e->max_batch; ++s) { release_slot(e, s); e->slot_released[s] = 0; }
     e->n_live = (int)n_seq;
     // slot state on the device
     const int cap = e->st.tok_cap, words = m.V / 32;
@@ -974,7 +977,8 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     m.eps = cfg->rms_eps; m.scale = 1.0f / std::sqrt((float)hd);
     e->max_batch = (int)opt.max_batch;
     e->pages_per_seq = (m.ctx + kPage - 1) / kPage;
-    e->n_pages = opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq;
+    e->n_pages = (opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq) + 1;   // + the spare page
+    e->spare_page = (int)(e->n_pages - 1);
     if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);
@@ -1048,9 +1052,10 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             else { e->allocs.push_back(q); e->kv_pool = q; e->kv_bytes = bytes; }
         }
         (void)p;
-        e->free_pages.resize(e->n_pages);
-        for (long long i = 0; i < e->n_pages; ++i) e->free_pages[i] = (int)(e->n_pages - 1 - i);
+        e->free_pages.resize(e->n_pages - 1);
+        for (long long i = 0; i + 1 < e->n_pages; ++i) e->free_pages[i] = (int)(e->n_pages - 2 - i);
         e->slot_pages.assign(e->max_batch, {});
+        e->slot_released.assign(e->max_batch, 0);
         e->h_len_bound.assign(e->max_batch, 0);
         A(&e->d_block_table, (size_t)e->max_batch * e->pages_per_seq, &e->scratch_bytes);
     }
@@ -1143,7 +1148,7 @@ void sllm_engine_destroy(sllm_engine* e) {
 int sllm_engine_stats(sllm_engine* e, sllm_stats* s) {
     if (!e || !s) return SLLM_ERR_INVALID;
     s->weight_bytes = e->weight_bytes; s->kv_bytes = e->kv_bytes; s->scratch_bytes = e->scratch_bytes;
-    s->kv_pages_total = (uint64_t)e->n_pages; s->kv_pages_free = e->free_pages.size();
+    s->kv_pages_total = (uint64_t)e->n_pages - 1; s->kv_pages_free = e->free_pages.size();
     s->launches = e->launches; s->decode_steps = e->decode_steps; s->last_step_ms = e->last_step_ms;
     return SLLM_OK;
 }
@@ -1345,6 +1350,67 @@ int sllm_truncate(sllm_engine* e, uint32_t slot, uint64_t n_tokens) {
     CU(cudaMemcpyAsync(e->d_dec_slot + slot, &slot_i, 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaStreamSynchronize(e->stream));
     e->h_len_bound[slot] = n;
+    return SLLM_OK;
+}
+
+// ---- single slots: the building blocks of continuous batching ---------------------------------------------
+static int park_slot(sllm_engine* e, int slot) {          // idle slot: finished, spare page everywhere, harmless pass inputs
+    release_slot(e, slot);
+    e->slot_released[slot] = 1;
+    std::vector<int> row(e->pages_per_seq, e->spare_page);
+    const int one = 1, zero = 0; const uint32_t zid = 0;
+    CU(cudaMemcpyAsync(e->d_block_table + (size_t)slot * e->pages_per_seq, row.data(), row.size() * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished + slot, &one, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.n_tok + slot, &one, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_slot + slot, &slot, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_pos + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_dec_id + slot, &zid, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return SLLM_OK;
+}
+
+int sllm_slot_assign(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_t len) {
+    if (!e || !ids) return fail(e, SLLM_ERR_INVALID, "sllm_slot_assign: null argument");
+    const ModelDims& m = e->md;
+    if (slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_CAPACITY, "sllm_slot_assign: slot exceeds max_batch");
+    if (len == 0) return fail(e, SLLM_ERR_INVALID, "Inference::generate: prompt encoded to zero tokens");
+    if (len > (uint32_t)m.ctx) return fail(e, SLLM_ERR_INVALID, "Model::forward: seq_len exceeds context_length");
+    for (uint32_t i = 0; i < len; ++i)
+        if (ids[i] >= (uint32_t)m.V) return fail(e, SLLM_ERR_INVALID, "token id outside the vocabulary");
+    for (int s = e->n_live; s < (int)slot; ++s) { int rc = park_slot(e, s); if (rc) return rc; }   // slots skipped over stay idle
+    e->n_live = std::max(e->n_live, (int)slot + 1);
+    release_slot(e, (int)slot);
+    e->slot_released[slot] = 0;
+    const int cap = e->st.tok_cap, words = m.V / 32;
+    std::vector<uint32_t> toks(cap, 0), seen(words, 0);
+    for (uint32_t i = 0; i < len; ++i) { toks[i] = ids[i]; seen[ids[i] >> 5] |= 1u << (ids[i] & 31); }
+    const int n = (int)len, zero = 0;
+    bool changed = false;
+    e->h_len_bound[slot] = n;
+    int rc = ensure_pages(e, (int)slot, n, &changed);
+    if (rc) return rc;
+    rc = upload_block_table(e, (int)slot);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(e->st.tokens + (size_t)slot * cap, toks.data(), (size_t)cap * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.seen + (size_t)slot * words, seen.data(), (size_t)words * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.n_tok + slot, &n, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.draw_idx + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    const int sl = (int)slot;
+    return prefill_impl(e, ids, &len, 1, nullptr, &sl);
+}
+
+int sllm_slot_release(sllm_engine* e, uint32_t slot) {
+    if (!e || slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_slot_release: bad slot");
+    if ((int)slot >= e->n_live) return SLLM_OK;
+    return park_slot(e, (int)slot);
+}
+
+int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n) {
+    if (!e || !flags || n > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_get_finished: bad argument");
+    CU(cudaMemcpyAsync(flags, e->st.finished, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
     return SLLM_OK;
 }
 
