@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the token loop on B200: decode tokens/s against the HBM roofline.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4s] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4] [--impl reference]
 
 Default workload (N=1): BASELINE config 2 -- the 100.3M model, batch 1, a prompt of 256 uniform
 random ids, 512 sampled decode steps (temperature 0.8, top-p 0.95, repetition penalty 1.15,

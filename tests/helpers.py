@@ -15,6 +15,8 @@ SMALL_EOS = 506
 MID = Config(vocab=1024, context=256, layers=3, d_model=128, heads=4, ffn=200)      # 4 KV pages: split-K path
 ODD = Config(vocab=256, context=96, layers=2, d_model=48, heads=3, ffn=40, theta=500.0, eps=1e-6)
 FULL = Config()
+# BASELINE config 5's layer shape (d=1536, 24 heads x 64, SwiGLU 4096) with 2 layers and a small vocabulary
+WIDE = Config(vocab=2048, context=192, layers=2, d_model=1536, heads=24, ffn=4096)
 
 
 def to_model_config(c: Config) -> ModelConfig:

@@ -13,7 +13,7 @@ import pytest
 
 from oracle.binding import OracleSession, greedy, prompt_ids, sample, uniforms
 from small_llm_b200 import SamplingOptions, SllmError
-from tests.helpers import FULL, MID, ODD, SMALL, SMALL_EOS, make_pair, rel_err
+from tests.helpers import FULL, MID, ODD, SMALL, SMALL_EOS, WIDE, make_pair, rel_err
 
 pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
@@ -57,6 +57,29 @@ def test_decode_steps_equal_prefill_rows(cfg, fp32, tol):
         worst = max(worst, rel_err(eng.step_logits(0), ref[t]))
     assert worst <= tol
     assert np.array_equal(eng.tokens(0), ids)
+
+
+@pytest.mark.parametrize("fp32,tol", [(True, TOL_F32), (False, TOL_BF16)])
+def test_wide_layer_shape_of_config5(fp32, tol):
+    """The 0.73B configuration's layer shape (d_model 1536, 24 heads, ffn 4096) through prefill, the fused
+    single-token decode path and a small batch."""
+    cfg = WIDE
+    o, eng = make_pair(cfg, seed=5, stddev=0.02, fp32=fp32, max_batch=3, via_checkpoint=False)
+    ids = prompt_ids(21, 3 * 100, cfg.vocab)
+    ref = o.forward(ids, 3, 100)
+    assert rel_err(eng.forward_logits(ids, 3, 100), ref) <= tol
+    # decode steps, teacher-forced: slot 0 alone (fused path), then three slots together
+    for n_slots in (1, 3):
+        prompts = [ids[s * 100: s * 100 + 70] for s in range(n_slots)]
+        eng.prefill(prompts)
+        opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
+        for t in range(70, 100):
+            eng.sample(opt, eos=cfg.vocab + 1)
+            for s in range(n_slots):
+                eng.force_token(s, int(ids[s * 100 + t]))
+            eng.decode_step()
+            for s in range(n_slots):
+                assert rel_err(eng.step_logits(s), ref[s, t]) <= tol, (n_slots, s, t)
 
 
 def test_batched_ragged_prefill_and_decode():
@@ -236,8 +259,9 @@ def test_config1_greedy_100m_bf16_and_fp32():
             eng.decode_step()
     msg = f"config1 bf16: prefill rel err {err_prefill:.2e}, decode rel err {worst:.2e}, greedy flips (step, ref margin) {flips}"
     print(msg)
-    if os.path.isdir("gpurun_out"):
-        open("gpurun_out/config1_parity.txt", "w").write(msg + "\n")
+    report_dir = os.environ.get("SLLM_REPORT_DIR")
+    if report_dir and os.path.isdir(report_dir):
+        open(os.path.join(report_dir, "config1_parity.txt"), "w").write(msg + "\n")
     assert err_prefill <= TOL_BF16 and worst <= TOL_BF16
     assert all(m < 1e-2 for _, m in flips), flips
     # fp32 weights: the free-running greedy stream is the oracle's stream
@@ -249,3 +273,31 @@ def test_config1_greedy_100m_bf16_and_fp32():
         first = int(np.argmax(got != ref_stream))
         _, margin = greedy(ref_logits[first - n_prompt], prompt, 1.0)
         assert margin < 1e-4, (first, margin)
+
+
+def test_config3_batch64_subset_against_oracle():
+    """BASELINE config 3 shape: 100.3M model, bf16, 64 sequences with 512-id prompts (seed 3), greedy decode.
+    The oracle (fp32) is run on a stated subset -- sequences 0, 21 and 63 -- teacher-forced on the engine's own
+    streams: every engine token must be the oracle's arg-max at that step unless the oracle's top-2 margin
+    there is below 1e-2; logits of the last prompt position within 2e-2."""
+    cfg = FULL
+    n_seq, n_prompt, n_new = 64, 512, 48
+    o, eng = make_pair(cfg, seed=0, stddev=0.02, fp32=False, max_batch=n_seq)
+    all_ids = prompt_ids(3, n_seq * n_prompt)
+    prompts = [all_ids[i * n_prompt:(i + 1) * n_prompt] for i in range(n_seq)]
+    opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
+    eng.prefill(prompts)
+    first_logits = {s: eng.step_logits(s) for s in (0, 21, 63)}
+    streams = eng.generate(prompts, n_new, opt)
+    assert all(len(x) == n_prompt + n_new for x in streams)
+    flips = []
+    for s in (0, 21, 63):
+        st = streams[s]
+        ref = o.forward(st[:-1], 1, len(st) - 1, row_from=n_prompt - 1)[0]
+        assert rel_err(first_logits[s], ref[0]) <= TOL_BF16
+        for i in range(n_new):
+            want, margin = greedy(ref[i], st[:n_prompt + i], 1.0)
+            if int(st[n_prompt + i]) != want:
+                flips.append((s, i, margin))
+    assert all(m < 1e-2 for _, _, m in flips), flips
+    assert len(flips) <= 6, flips
