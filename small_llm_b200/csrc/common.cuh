@@ -102,6 +102,7 @@ struct PassView {
     int n_tok;
     const PfTile* tiles;      // prefill passes: runs of consecutive positions, <= 64 queries each (else null)
     int n_tiles;
+    const int* order;         // optional permutation, grid index -> pass token, longest context first (else null)
 };
 
 struct KvView {

@@ -98,6 +98,8 @@ struct sllm_engine {
     int pass_cap = 0;                  // tokens per pass
     uint32_t* d_tok_id = nullptr; int* d_tok_slot = nullptr; int* d_tok_pos = nullptr;
     uint32_t* d_dec_id = nullptr; int* d_dec_slot = nullptr; int* d_dec_pos = nullptr;   // decode pass (written by the sampler)
+    int* d_attn_order = nullptr;       // decode pass: slots by descending length, the attention grid's block order
+    std::vector<int> h_attn_order;
     float* x = nullptr; float* q = nullptr; float* att = nullptr; float* hid = nullptr;
     int* d_row_tok = nullptr;
     PfTile* d_tiles = nullptr;
@@ -647,7 +649,27 @@ int grow_for_step(sllm_engine* e) {
     return SLLM_OK;
 }
 
-PassView decode_view(sllm_engine* e) { return PassView{e->d_dec_id, e->d_dec_slot, e->d_dec_pos, e->n_live, nullptr, 0}; }
+// With many more (token, head) blocks than the GPU holds at once, the attention kernel's last wave should be
+// its shortest blocks: the decode pass hands it the slots sorted by descending length.
+bool decode_uses_order(const sllm_engine* e) { return e->n_live * e->md.H >= 16 * e->sm_count; }
+
+PassView decode_view(sllm_engine* e) {
+    return PassView{e->d_dec_id, e->d_dec_slot, e->d_dec_pos, e->n_live, nullptr, 0,
+                    decode_uses_order(e) ? e->d_attn_order : nullptr};
+}
+
+// Lengths grow in step, so the order computed from the host's bounds stays right for a whole run of iterations;
+// it is a scheduling hint only (any permutation gives the same results).
+int refresh_attn_order(sllm_engine* e) {
+    if (!decode_uses_order(e)) return SLLM_OK;
+    e->h_attn_order.resize(e->n_live);
+    for (int i = 0; i < e->n_live; ++i) e->h_attn_order[i] = i;
+    std::stable_sort(e->h_attn_order.begin(), e->h_attn_order.end(),
+                     [&](int x, int y) { return e->h_len_bound[x] > e->h_len_bound[y]; });
+    CU(cudaMemcpyAsync(e->d_attn_order, e->h_attn_order.data(), (size_t)e->n_live * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));           // the host vector may change before the copy would otherwise run
+    return SLLM_OK;
+}
 
 // One decode iteration = sampler, then the model over the sampled tokens.
 int enqueue_iteration(sllm_engine* e, const SampleArgs& s) {
@@ -1070,6 +1092,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->d_tok_id, e->pass_cap, &e->scratch_bytes); A(&e->d_tok_slot, e->pass_cap, &e->scratch_bytes);
     A(&e->d_tok_pos, e->pass_cap, &e->scratch_bytes);
     A(&e->d_dec_id, e->max_batch, &e->scratch_bytes); A(&e->d_dec_slot, e->max_batch, &e->scratch_bytes);
+    A(&e->d_attn_order, e->max_batch, &e->scratch_bytes);
     A(&e->d_dec_pos, e->max_batch, &e->scratch_bytes);
     A(&e->d_row_tok, e->pass_cap, &e->scratch_bytes);
     A(&e->d_tiles, e->pass_cap, &e->scratch_bytes);
@@ -1268,8 +1291,10 @@ int sllm_sample(sllm_engine* e, const sllm_sampling* opt, const double* draws) {
 int sllm_decode_step(sllm_engine* e) {
     if (!e) return SLLM_ERR_INVALID;
     if (e->n_live == 0) return fail(e, SLLM_ERR_STATE, "sllm_decode_step: no live slots");
+    int rc = refresh_attn_order(e);
+    if (rc) return rc;
     CU(cudaEventRecord(e->ev0, e->stream));
-    int rc = run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, false);
+    rc = run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, false);
     if (rc) return rc;
     CU(cudaEventRecord(e->ev1, e->stream));
     CU(cudaStreamSynchronize(e->stream));
@@ -1419,6 +1444,7 @@ static int decode_loop_impl(sllm_engine* e, uint64_t n_steps, const sllm_samplin
                             int seeded, bool last_pass, bool* all_done_out) {
     SampleArgs s = make_sample_args(e, opt, e->n_live, d_draws, stride, seeded);
     cudaGraphExec_t ge = nullptr;
+    { int rc = refresh_attn_order(e); if (rc) return rc; }
     if (e->opt.use_graph) { int rc = get_iteration_graph(e, s, &ge); if (rc) return rc; }
     const uint64_t check_every = 64;
     for (uint64_t i = 0; i < n_steps; ++i) {
@@ -1570,6 +1596,14 @@ int attn_decode_launch(sllm_engine* e, uint32_t layer, uint32_t n_tok, const flo
     t.keys_per_split = pages_per_split * kPage;
     t.n_splits = (e->pages_per_seq + pages_per_split - 1) / pages_per_split;
     t.part_o = part_o; t.part_ml = part_ml; t.ticket = ticket;
+    if ((int)n_tok > e->split_tok_cap) {
+        // many tokens (n_splits is 1 here): the page-streaming kernel the engine itself uses at large batch
+        cudaStream_t own = e->stream;
+        e->stream = stream;
+        const int rc = e->f32 ? launch_attn<float>(e, t, false) : launch_attn<__nv_bfloat16>(e, t, false);
+        e->stream = own;
+        return rc;
+    }
     const dim3 grid(t.n_splits, m.H, n_tok), block(kAttnThreads);
     void (*kern)(AttnDecArgs) = nullptr;
     if (e->f32) {

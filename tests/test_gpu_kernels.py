@@ -2,9 +2,9 @@
 import numpy as np
 import pytest
 
-from oracle.binding import prompt_ids
+from oracle.binding import Config, prompt_ids
 from small_llm_b200 import SllmError
-from tests.helpers import MID, make_pair
+from tests.helpers import MID, ODD, WIDE, make_pair
 
 pytestmark = pytest.mark.gpu
 
@@ -47,3 +47,36 @@ def test_attention_kernel_split_invariance_and_checks():
         eng.k_attn_decode(0, 3, q.data_ptr(), slot.data_ptr(), pos.data_ptr(), 33, out2.data_ptr())
     with pytest.raises(ValueError, match="null device pointer"):
         eng.k_attn_decode(0, 3, 0, slot.data_ptr(), pos.data_ptr(), 1, out2.data_ptr())
+
+
+HD128 = Config(vocab=256, context=192, layers=1, d_model=256, heads=2, ffn=64)
+
+
+@pytest.mark.parametrize("cfg,fp32", [(MID, False), (MID, True), (ODD, False), (ODD, True), (WIDE, False), (HD128, False),
+                                      (HD128, True)],
+                         ids=["hd32-bf16", "hd32-f32", "hd16-bf16", "hd16-f32", "hd64-bf16", "hd128-bf16", "hd128-f32"])
+def test_streaming_attention_matches_split_kernel(cfg, fp32):
+    """More than 64 tokens take the page-streaming kernel (each warp owns a quarter of every page); up to 64
+    take the per-lane kernel.  Same queries, every position of a prompt that ends inside a page: the two
+    must agree to rounding, whatever quarter of the last page a position falls in."""
+    import torch
+    o, eng = make_pair(cfg, seed=5, stddev=0.05, fp32=fp32, via_checkpoint=False)
+    n_prompt = min(cfg.context - 3, 171)
+    eng.prefill([prompt_ids(6, n_prompt, cfg.vocab)])
+    n_tok = n_prompt
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(n_tok, cfg.d_model, device="cuda", generator=g)
+    slot = torch.zeros(n_tok, dtype=torch.int32, device="cuda")
+    pos = torch.arange(n_tok, dtype=torch.int32, device="cuda")
+    layer = cfg.layers - 1
+    out_stream = torch.full((n_tok, cfg.d_model), float("nan"), device="cuda")
+    eng.k_attn_decode(layer, n_tok, q.data_ptr(), slot.data_ptr(), pos.data_ptr(), 1, out_stream.data_ptr())
+    out_ref = torch.full((n_tok, cfg.d_model), float("nan"), device="cuda")
+    for b in range(0, n_tok, 64):
+        n = min(64, n_tok - b)
+        eng.k_attn_decode(layer, n, q[b:].data_ptr(), slot[b:].data_ptr(), pos[b:].data_ptr(), 1, out_ref[b:].data_ptr())
+    torch.cuda.synchronize()
+    a, r = out_stream.cpu().numpy(), out_ref.cpu().numpy()
+    assert np.isfinite(a).all()
+    assert np.abs(a - r).max() <= 4e-6 * np.abs(r).max() + 1e-7
+    assert np.array_equal(a[0], r[0])          # one key: the value row itself
