@@ -6,8 +6,8 @@
 //
 // The weight tile is the MMA's M side (128 rows = 128 TMEM lanes), the token tile its N side
 // (32..256 columns), so the batch does not have to fill a 128-row tile.  One thread block computes
-// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
-// epilogue (each reads its 32 TMEM lanes; thread = weight row, registers = tokens).  The same fused
+// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..9 =
+// epilogue (each reads 32 TMEM lanes of one half of the columns; thread = weight row, registers = tokens).  The same fused
 // epilogues as the GEMV family: RoPE + paged-KV append, residual add, SiLU(gate)*up, fp32 logits.
 // Every mbarrier wait is bounded; on expiry the block raises the engine's status word, lets its
 // copies land, frees its tensor memory and returns.
@@ -21,7 +21,7 @@ namespace sllm {
 
 constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
 constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // a wait gives up after two seconds
 
 struct TcArgs {
@@ -98,6 +98,17 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
                  : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+template <int CW> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t* r) {
+    if (CW == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
+}
 
 template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
 template <int BN> __host__ __device__ constexpr size_t tc_smem_bytes() {
@@ -115,7 +126,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     uint8_t* sB = smem + STAGES * A_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[S], empty[S], done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
-    int* tok_meta = reinterpret_cast<int*>(tmem_slot + 2);                  // [4 epilogue warps][pos[BN] | page[BN]]
+    int* tok_meta = reinterpret_cast<int*>(tmem_slot + 2);                  // [8 epilogue warps][pos[BN/2] | page[BN/2]]
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -136,6 +147,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    SLLM_TL(500 + MODE * 10);
     pdl_launch_dependents();
     // The weight tiles do not depend on the predecessor kernel: the first STAGES of them are requested before
     // the dependency wait (the barrier already expects the bytes of both operands of its stage).
@@ -147,6 +159,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         }
     }
     pdl_wait();
+    SLLM_TL(501 + MODE * 10);
 
     bool ok = true;
     if (warp == 0) {
@@ -170,6 +183,13 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, a.status, 12);
                 if (!ok) break;
                 tc_fence_after();
+#ifdef SLLM_TIMELINE
+                if (kb == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+                    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                    const unsigned int i = atomicAdd(&g_tl_n, 1u);
+                    if (i < (1u << 15)) { g_tl_buf[2 * i] = 502 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
+                }
+#endif
                 const uint32_t aaddr = smem_u32(sA + s * A_BYTES), baddr = smem_u32(sB + s * B_BYTES);
 #pragma unroll
                 for (int k = 0; k < kTcBK / 16; ++k)
@@ -179,20 +199,25 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
             if (ok) tc_commit(done_bar);            // accumulator complete
         }
     } else {
-        // ---- epilogue: warps 2..5 own TMEM lane quarters 2,3,0,1 ---------------------------------------
+        // ---- epilogue: warps 2..9; warp w reads TMEM lane quarter w % 4, columns of half (w - 2) / 4 -------
+        constexpr int HALF = BN / 2;                             // token columns per epilogue warp
+        constexpr int CW = HALF >= 32 ? 32 : 16;                 // columns per TMEM load
+        const int ew = warp - 2;
         const int quarter = warp & 3;
+        const int cbeg = (ew >> 2) * HALF;
         const int row = m0 + quarter * 32 + lane;
         const bool row_ok = row < a.R;
         const int D = a.m.D, hd = a.m.hd;
         int which = 0, col = 0, head = 0, d = 0;
         if (MODE == kModeQKV && row_ok) { which = row / D; col = row - which * D; head = col / hd; d = col - head * hd; }
-        // While the tensor cores work, each epilogue warp fetches the positions and KV pages of the tile's
-        // tokens into its own shared-memory copy, so the epilogue below has no dependent global loads.
-        int* my_pos = tok_meta + (warp - 2) * 2 * BN;
-        int* my_page = my_pos + BN;
+        // While the tensor cores work, each epilogue warp fetches the positions and KV pages of its tokens into
+        // its own shared-memory copy, and the operands of its first column chunk that do not depend on the
+        // accumulator (rotation factors, residual values), so that little is left to wait for afterwards.
+        int* my_pos = tok_meta + ew * BN;
+        int* my_page = my_pos + HALF;
         if (MODE == kModeQKV) {
-            for (int j = lane; j < BN; j += 32) {
-                const int tok = t0 + j;
+            for (int j = lane; j < HALF; j += 32) {
+                const int tok = t0 + cbeg + j;
                 int pos = 0, page = 0;
                 if (tok < a.n_tok) {
                     pos = a.pass.tok_pos[tok];
@@ -202,74 +227,98 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
             }
             __syncwarp();
         }
+        float2 cs[MODE == kModeQKV ? CW : 1];
+        float xv[MODE == kModeResidual ? CW : 1];
+        auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
+            if (MODE == kModeQKV) {
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                    cs[j] = (which < 2 && row_ok) ? a.rope[(size_t)my_pos[c - cbeg + j] * (hd / 2) + (d >> 1)] : make_float2(1.f, 0.f);
+            } else if (MODE == kModeResidual) {
+#pragma unroll
+                for (int j = 0; j < CW; ++j) {
+                    const int tok = t0 + c + j;
+                    xv[j] = (row_ok && tok < a.n_tok) ? a.out[(size_t)tok * a.R + row] : 0.f;
+                }
+            }
+        };
+        if (t0 + cbeg < a.n_tok) fetch(cbeg);
         ok = mbar_wait(done_bar, 0, a.status, 13);
         ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
         tc_fence_after();
-        for (int c0 = 0; c0 < BN && ok; c0 += 32) {
-            if (t0 + c0 >= a.n_tok) break;                       // uniform over the block
-            uint32_t v[32];
-            tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+#ifdef SLLM_TIMELINE
+        if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+            unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            const unsigned int i = atomicAdd(&g_tl_n, 1u);
+            if (i < (1u << 15)) { g_tl_buf[2 * i] = 503 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
+        }
+#endif
+        for (int c0 = cbeg; c0 < cbeg + HALF && ok; c0 += CW) {
+            if (t0 + c0 >= a.n_tok) break;                       // uniform over the warp
+            const bool more = c0 + CW < cbeg + HALF && t0 + c0 + CW < a.n_tok;
+            uint32_t v[CW];
+            tc_ld<CW>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
             if (MODE == kModeResidual) {
-                // read-modify-write of the residual stream: 16 independent loads, then 16 stores
+                float r[CW];
 #pragma unroll
-                for (int jb = 0; jb < 32; jb += 16) {
-                    float xv[16];
+                for (int j = 0; j < CW; ++j) r[j] = xv[j] + __uint_as_float(v[j]);
+                if (more) fetch(c0 + CW);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = t0 + c0 + jb + j;
-                        xv[j] = (row_ok && tok < a.n_tok) ? a.out[(size_t)tok * a.R + row] : 0.f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = t0 + c0 + jb + j;
-                        if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = xv[j] + __uint_as_float(v[jb + j]);
-                    }
+                for (int j = 0; j < CW; ++j) {
+                    const int tok = t0 + c0 + j;
+                    if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = r[j];
                 }
             } else if (MODE == kModeHead) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c0 + j;
                     if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = __uint_as_float(v[j]);
                 }
             } else if (MODE == kModeGateUp) {
+                // (gate, up) sit in adjacent lanes; every lane evaluates the same branch-free expression so that
+                // the columns overlap in the pipeline, and the even lanes store
+                const bool store_lane = row_ok && (row & 1) == 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int tok = t0 + c0 + j;
+                for (int j = 0; j < CW; ++j) {
                     const float acc = __uint_as_float(v[j]);
-                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);      // (gate, up) sit in adjacent lanes
-                    if (row_ok && tok < a.n_tok && (row & 1) == 0) {
-                        const float sig = 1.0f / (1.0f + expf(-acc));
-                        a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn((acc * sig) * other);
-                    }
+                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                    const float hval = __fdividef(acc, 1.0f + __expf(-acc)) * other;
+                    const int tok = t0 + c0 + j;
+                    if (store_lane && tok < a.n_tok) a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn(hval);
                 }
             } else {
-                // RoPE pairs sit in adjacent lanes; factors are fetched 8 tokens at a time
+                // RoPE pairs sit in adjacent lanes
+                float r[CW];
 #pragma unroll
-                for (int jb = 0; jb < 32; jb += 8) {
-                    float2 cs[8];
+                for (int j = 0; j < CW; ++j) {
+                    const float acc = __uint_as_float(v[j]);
+                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                    r[j] = acc;
+                    if (which < 2) r[j] = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
+                }
+                if (more) fetch(c0 + CW);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        cs[j] = (which < 2 && row_ok) ? a.rope[(size_t)my_pos[c0 + jb + j] * (hd / 2) + (d >> 1)] : make_float2(1.f, 0.f);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int tok = t0 + c0 + jb + j;
-                        const float acc = __uint_as_float(v[jb + j]);
-                        const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
-                        if (!row_ok || tok >= a.n_tok) continue;
-                        float o = acc;
-                        if (which < 2) o = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
-                        if (which == 0) {
-                            a.out[(size_t)tok * D + col] = o;
-                        } else {
-                            const int pos = my_pos[c0 + jb + j];
-                            kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, my_page[c0 + jb + j], which - 1, head, pos % kPage)[d] =
-                                __float2bfloat16_rn(o);
-                        }
+                for (int j = 0; j < CW; ++j) {
+                    const int tok = t0 + c0 + j;
+                    if (!row_ok || tok >= a.n_tok) continue;
+                    if (which == 0) {
+                        a.out[(size_t)tok * D + col] = r[j];
+                    } else {
+                        const int pos = my_pos[c0 - cbeg + j];
+                        kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, my_page[c0 - cbeg + j], which - 1, head, pos % kPage)[d] =
+                            __float2bfloat16_rn(r[j]);
                     }
                 }
             }
         }
     }
+#ifdef SLLM_TIMELINE
+    if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+        unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const unsigned int i = atomicAdd(&g_tl_n, 1u);
+        if (i < (1u << 15)) { g_tl_buf[2 * i] = 504 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
+    }
+#endif
     if (!ok) {                       // a wait gave up: give copies in flight time to land before shared memory goes away
         for (int i = 0; i < 64; ++i) __nanosleep(16384);
     }
@@ -288,6 +337,7 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bf16(const float* __restrict__ 
                                                        __nv_bfloat16* __restrict__ out, int D, float eps, const int* row_tok,
                                                        const float* emb, const uint32_t* tok_id, float* x_out) {
     __shared__ float red[8];
+    SLLM_TL(700);
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
