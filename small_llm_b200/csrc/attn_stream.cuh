@@ -14,7 +14,7 @@
 namespace sllm {
 
 constexpr int kStreamThreads = 128;
-constexpr int kStreamStages = 3;
+constexpr int kStreamStages = 3;         // pages in flight per warp (6 measured slower at 32..64 sequences: fewer blocks fit an SM)
 
 __device__ __forceinline__ uint32_t as_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -72,7 +72,7 @@ template <int DL> __device__ __forceinline__ void load_vals(const float* p, floa
 // Each of the four warps owns a quarter of every page (16 consecutive keys and their values) and runs its own
 // copy pipeline over it: own stages, own mbarriers, own running softmax state.  The main loop therefore has no
 // block-wide barrier; the four states are merged once at the end.
-template <typename KVT, int HD>
+template <typename KVT, int HD, int ST>
 __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArgs a, unsigned int* status) {
     constexpr int EPC = Elems<KVT>::per16;
     constexpr int LPK = HD / EPC;                 // lanes per key in the score phase
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     static_assert(LPK >= 2 && LPK <= 32 && KW % KPI == 0 && KPI % KGW == 0, "unsupported head_dim");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];   // [warp][stage][K rows | V rows]
-    __shared__ __align__(8) unsigned long long bars[WARPS][kStreamStages];
+    __shared__ __align__(8) unsigned long long bars[WARPS][ST];
     __shared__ float red_o[WARPS][HD];
     __shared__ float red_m[WARPS], red_l[WARPS];
     __shared__ float s_q[HD];
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
 
     if (tid == 0) {
         for (int w = 0; w < WARPS; ++w)
-            for (int s = 0; s < kStreamStages; ++s) bar_init(as_smem(&bars[w][s]), 1);
+            for (int s = 0; s < ST; ++s) bar_init(as_smem(&bars[w][s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_ok = 1;
     }
@@ -124,13 +124,20 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     for (int i = tid; i < n_pages && i < kTableCache; i += kStreamThreads) s_table[i] = table[i];
     __syncthreads();
 
+#ifdef SLLM_TIMELINE
+    unsigned long long tl_loc[40]; int tl_n = 0;
+#define TL_LOC() do { if (tl_n < 40) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); tl_loc[tl_n++] = t_; } } while (0)
+#else
+#define TL_LOC()
+#endif
+    TL_LOC();
     const int wk0 = warp * KW;                                    // this warp's first key inside a page
     // the last page may hold fewer keys than this warp's offset: then the warp has one page less
     const int last_nk = n_pages > 0 ? min(kPage, pos + 1 - (pg0 + n_pages - 1) * kPage) : 0;
     const int my_pages = n_pages - ((n_pages > 0 && last_nk <= wk0) ? 1 : 0);
-    unsigned char* my_smem = smem_raw + (size_t)warp * kStreamStages * 2 * WBLK;
+    unsigned char* my_smem = smem_raw + (size_t)warp * ST * 2 * WBLK;
     auto issue = [&](int pg) {                    // one lane: this warp's K and V rows of page pg into stage pg % stages
-        const int s = pg % kStreamStages;
+        const int s = pg % ST;
         const int page = pg < kTableCache ? s_table[pg] : table[pg];
         const uint32_t bar = as_smem(&bars[warp][s]);
         bar_expect(bar, 2 * WBLK);
@@ -138,7 +145,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         bulk_g2s(as_smem(my_smem + (size_t)s * 2 * WBLK + WBLK), kv_ptr<KVT>(a.kv, a.m, a.layer, page, 1, head, wk0), WBLK, bar);
     };
     if (lane == 0)
-        for (int pg = 0; pg < kStreamStages && pg < my_pages; ++pg) issue(pg);
+        for (int pg = 0; pg < ST && pg < my_pages; ++pg) issue(pg);
 
     const int sub = lane % LPK, grp = lane / LPK;
     float qf[EPC];
@@ -151,10 +158,11 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
 
     bool ok = true;
     for (int pg = 0; pg < my_pages; ++pg) {
-        const int s = pg % kStreamStages;
-        ok = bar_wait(as_smem(&bars[warp][s]), (pg / kStreamStages) & 1);
+        const int s = pg % ST;
+        ok = bar_wait(as_smem(&bars[warp][s]), (pg / ST) & 1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        TL_LOC();
         const KVT* Kp = reinterpret_cast<const KVT*>(my_smem + (size_t)s * 2 * WBLK);
         const KVT* Vp = reinterpret_cast<const KVT*>(my_smem + (size_t)s * 2 * WBLK + WBLK);
         const int nkw = pos + 1 - (pg0 + pg) * kPage - wk0;     // valid keys among this warp's KW (>= 1)
@@ -210,8 +218,9 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
                 }
         }
         __syncwarp();                                            // every lane is done with stage s
-        if (lane == 0 && pg + kStreamStages < my_pages) issue(pg + kStreamStages);
+        if (lane == 0 && pg + ST < my_pages) issue(pg + ST);
     }
+    TL_LOC();
     if (!ok) { s_ok = 0; atomicExch(status, 21u); }
     // merge the four warps' states
 #pragma unroll
@@ -230,6 +239,14 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         for (int i = 0; i < 32; ++i) __nanosleep(16384);
         return;
     }
+    TL_LOC();
+#ifdef SLLM_TIMELINE
+    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        const unsigned int i0 = atomicAdd(&g_tl_n, (unsigned int)tl_n);
+        for (int i = 0; i < tl_n; ++i)
+            if (i0 + i < (1u << 15)) { g_tl_buf[2 * (i0 + i)] = 610 + i; g_tl_buf[2 * (i0 + i) + 1] = tl_loc[i]; }
+    }
+#endif
     float blk_m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) blk_m = fmaxf(blk_m, red_m[w]);
@@ -277,8 +294,8 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     if (tid == 0) a.ticket[(size_t)tok * a.m.H + head] = 0;
 }
 
-template <typename KVT, int HD> constexpr size_t attn_stream_smem() {
-    return (size_t)kStreamStages * 2 * kPage * HD * sizeof(KVT);
+template <typename KVT, int HD, int ST> constexpr size_t attn_stream_smem() {
+    return (size_t)ST * 2 * kPage * HD * sizeof(KVT);
 }
 
 }  // namespace sllm

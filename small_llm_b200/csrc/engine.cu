@@ -123,6 +123,7 @@ struct sllm_engine {
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
+    int tune_stream_splits = 0;        // SLLM_STREAM_SPLITS: tuning aid, overrides the split count of the streaming kernel
     unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
     float* samp_w = nullptr; float* samp_pmax_val = nullptr; int* samp_pmax_idx = nullptr;
     int samp_bps_cap = 128;
@@ -230,8 +231,8 @@ int launch_gemv(sllm_engine* e, GemvArgs a, bool pdl) {
 
 template <typename KVT, int HD>
 int launch_attn_stream_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
-    return launch(e, k_attn_stream<KVT, HD>, dim3(a.n_splits, a.m.H, a.pass.n_tok), dim3(kStreamThreads), attn_stream_smem<KVT, HD>(),
-                  pdl, a, e->d_status);
+    return launch(e, k_attn_stream<KVT, HD, kStreamStages>, dim3(a.n_splits, a.m.H, a.pass.n_tok), dim3(kStreamThreads),
+                  attn_stream_smem<KVT, HD, kStreamStages>(), pdl, a, e->d_status);
 }
 
 template <typename KVT, int HD>
@@ -419,8 +420,16 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
         if (rc) return rc;
         AttnDecArgs t{};
         t.q = e->q; t.out = e->att; t.out_bf16 = e->att16; t.m = m; t.kv = kv; t.pass = pv; t.layer = l;
-        // few (token, head) pairs: split each one's pages over up to 4 blocks so that every SM has ~8 blocks
-        t.n_splits = (pv.n_tiles == 0 && n <= e->split_tok_cap) ? std::max(1, std::min(4, (8 * e->sm_count) / (n * m.H))) : 1;
+        // few (token, head) pairs: split each one's pages over up to 4 blocks, about 8 blocks per SM in all
+        // (measured at 32 and 64 sequences: 4 splits and 1 split are the fastest); none once the pairs alone
+        // fill the 4 resident blocks per SM
+        {
+            const int pairs = n * m.H;
+            t.n_splits = 1;
+            if (pv.n_tiles == 0 && n <= e->split_tok_cap && pairs < 4 * e->sm_count)
+                t.n_splits = std::max(1, std::min(4, (8 * e->sm_count + pairs / 2) / pairs));
+        }
+        if (e->tune_stream_splits > 0 && pv.n_tiles == 0 && n <= e->split_tok_cap) t.n_splits = e->tune_stream_splits;
         t.keys_per_split = e->pages_per_seq * kPage;
         t.part_o = e->part_o; t.part_ml = e->part_ml; t.ticket = e->ticket;
         rc = launch_attn_any(e, t, pdl);
@@ -552,10 +561,10 @@ int configure_kernels_t(sllm_engine* e) {
     if (!rc) rc = big(k_attn_prefill<WT, 32>, attn_prefill_smem<WT, 32>());
     if (!rc) rc = big(k_attn_prefill<WT, 64>, attn_prefill_smem<WT, 64>());
     if (!rc) rc = big(k_attn_prefill<WT, 128>, attn_prefill_smem<WT, 128>());
-    if (!rc) rc = big(k_attn_stream<WT, 16>, attn_stream_smem<WT, 16>());
-    if (!rc) rc = big(k_attn_stream<WT, 32>, attn_stream_smem<WT, 32>());
-    if (!rc) rc = big(k_attn_stream<WT, 64>, attn_stream_smem<WT, 64>());
-    if (!rc) rc = big(k_attn_stream<WT, 128>, attn_stream_smem<WT, 128>());
+    if (!rc) rc = big(k_attn_stream<WT, 16, kStreamStages>, attn_stream_smem<WT, 16, kStreamStages>());
+    if (!rc) rc = big(k_attn_stream<WT, 32, kStreamStages>, attn_stream_smem<WT, 32, kStreamStages>());
+    if (!rc) rc = big(k_attn_stream<WT, 64, kStreamStages>, attn_stream_smem<WT, 64, kStreamStages>());
+    if (!rc) rc = big(k_attn_stream<WT, 128, kStreamStages>, attn_stream_smem<WT, 128, kStreamStages>());
     if (rc) return rc;
     rc = configure_gemv<WT, kModeQKV>(e);
     if (!rc) rc = configure_gemv<WT, kModeResidual>(e);
@@ -1002,6 +1011,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     e->n_pages = (opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq) + 1;   // + the spare page
     e->spare_page = (int)(e->n_pages - 1);
     if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
+    if (const char* v = std::getenv("SLLM_STREAM_SPLITS")) e->tune_stream_splits = std::min(std::max(0, std::atoi(v)), 8);
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);
     e->logit_rows_cap = std::max(e->max_batch, 64);
@@ -1115,8 +1125,8 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             for (uint64_t l = 0; l < L; ++l) { unsigned char* p = nullptr; A(&p, D * F * ws, &e->weight_bytes); e->wdT[l] = p; }
         }
     }
-    A(&e->samp_mass, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
-    A(&e->samp_cnt, (size_t)e->max_batch * kSampBuckets, &e->scratch_bytes);
+    A(&e->samp_mass, (size_t)e->max_batch * kL0Buckets, &e->scratch_bytes);
+    A(&e->samp_cnt, (size_t)e->max_batch * kL0Buckets, &e->scratch_bytes);
     A(&e->samp_w, (size_t)e->max_batch * V, &e->scratch_bytes);
     A(&e->samp_pmax_val, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);
     A(&e->samp_pmax_idx, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);

@@ -110,7 +110,8 @@ template <int CW> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t
     if (CW == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
 }
 
-template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
+// as many stages as shared memory holds: a block's throughput is its bytes in flight over the copy latency
+template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10)); }
 template <int BN> __host__ __device__ constexpr size_t tc_smem_bytes() {
     return 1024 + (size_t)tc_stages<BN>() * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + 256 + 4 * 2 * BN * sizeof(int);
 }

@@ -25,7 +25,9 @@
 namespace sllm {
 
 constexpr int kSampThreads = 1024;
-constexpr int kSampBuckets = 1024;
+constexpr int kSampBuckets = 1024;              // buckets of a refinement histogram in shared memory
+constexpr int kL0Buckets = 8192;                // buckets of the level-0 histogram in global memory
+constexpr int kL0PerThread = kL0Buckets / kSampThreads;
 constexpr int kFixShift = 47;
 
 struct SeqState {                 // device arrays indexed by slot
@@ -105,16 +107,18 @@ struct SampScratch {
 
 struct SelectResult { uint32_t key; unsigned long long cum_above, qk; unsigned int cnt_above, ties, r; int found; };
 
-// Level-0 bucket of a weight key: 64 buckets per octave, bucket 1023 holds 1.0, bucket 0 everything below 2^-16.
-constexpr uint32_t kL0Shift = 17;
-constexpr uint32_t kL0Top = 0x3F800000u >> kL0Shift;          // 8128
+// Level-0 bucket of a weight key: 512 buckets per octave, the top bucket holds 1.0, bucket 0 everything below
+// 2^-16.  Narrow buckets keep the candidate lists short (tens of elements even when the distribution is flat)
+// and spread the histogram's reductions over many addresses.
+constexpr uint32_t kL0Shift = 14;
+constexpr uint32_t kL0Top = 0x3F800000u >> kL0Shift;          // 65024
 __device__ __forceinline__ int l0_bucket(uint32_t key) {
-    const int b = (int)(key >> kL0Shift) - (int)(kL0Top - (kSampBuckets - 1));
-    return b < 0 ? 0 : (b > kSampBuckets - 1 ? kSampBuckets - 1 : b);
+    const int b = (int)(key >> kL0Shift) - (int)(kL0Top - (kL0Buckets - 1));
+    return b < 0 ? 0 : (b > kL0Buckets - 1 ? kL0Buckets - 1 : b);
 }
 __device__ __forceinline__ void l0_range(int b, uint32_t& lo, uint32_t& hi) {
-    lo = b == 0 ? 0u : ((uint32_t)(b + (int)kL0Top - (kSampBuckets - 1)) << kL0Shift);
-    hi = (((uint32_t)(b + (int)kL0Top - (kSampBuckets - 1)) + 1u) << kL0Shift) - 1u;
+    lo = b == 0 ? 0u : ((uint32_t)(b + (int)kL0Top - (kL0Buckets - 1)) << kL0Shift);
+    hi = (((uint32_t)(b + (int)kL0Top - (kL0Buckets - 1)) + 1u) << kL0Shift) - 1u;
 }
 
 // Thread j holds bucket (top - j) of a histogram (my_m, my_c; zero when top - j < 0).  Picks the first
@@ -155,44 +159,128 @@ __device__ int scan_pick(unsigned long long my_m, unsigned int my_c, int top, Sa
     return top - pick;
 }
 
-// Finds the element, in descending (key, then ascending id) order, at which the running mass first reaches
-// `target`.  (l0_m, l0_c) is this thread's level-0 bucket (bucket 1023 - tid); h1 is working space.
-__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, unsigned long long l0_m, unsigned int l0_c,
-                                    SampHist& h1, SampScratch& s) {
+// A thread's share of the level-0 histogram: kL0PerThread consecutive buckets in descending order (k = 0 is
+// the highest), with the mass and count of everything above them.
+struct L0Regs {
+    unsigned long long m[kL0PerThread]; unsigned int c[kL0PerThread];
+    unsigned long long exc_m; unsigned int exc_c;
+};
+
+// Loads this thread's share of the slot's level-0 histogram and clears it for the next step.
+__device__ __forceinline__ void l0_load(unsigned long long* gm, unsigned int* gc, L0Regs& r) {
+    static_assert(kL0PerThread == 8, "vector loads below assume 8 buckets per thread");
     const int tid = threadIdx.x;
-    unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
+    const int base = kL0Buckets - kL0PerThread * (tid + 1);     // this thread's lowest bucket
+    ulonglong2 mm[4]; uint4 cc[2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mm[j] = __ldcg(reinterpret_cast<const ulonglong2*>(gm + base) + j);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) cc[j] = __ldcg(reinterpret_cast<const uint4*>(gc + base) + j);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { r.m[7 - 2 * j] = mm[j].x; r.m[6 - 2 * j] = mm[j].y; }
+    r.c[7] = cc[0].x; r.c[6] = cc[0].y; r.c[5] = cc[0].z; r.c[4] = cc[0].w;
+    r.c[3] = cc[1].x; r.c[2] = cc[1].y; r.c[1] = cc[1].z; r.c[0] = cc[1].w;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) reinterpret_cast<ulonglong2*>(gm + base)[j] = make_ulonglong2(0ull, 0ull);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(gc + base)[j] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Block-wide exclusive prefix of the level-0 histogram in descending bucket order; totals in s.tot_m / s.tot_c.
+__device__ void l0_scan(L0Regs& r, SampScratch& s) {
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    unsigned long long my_m = 0; unsigned int my_c = 0;
+#pragma unroll
+    for (int k = 0; k < kL0PerThread; ++k) { my_m += r.m[k]; my_c += r.c[k]; }
+    unsigned long long inc_m = my_m; unsigned int inc_c = my_c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long m2 = __shfl_up_sync(0xffffffffu, inc_m, o);
+        const unsigned int c2 = __shfl_up_sync(0xffffffffu, inc_c, o);
+        if (lane >= o) { inc_m += m2; inc_c += c2; }
+    }
+    if (lane == 31) { s.sc_m[wp] = inc_m; s.sc_c[wp] = inc_c; }
+    __syncthreads();
+    unsigned long long off_m = 0; unsigned int off_c = 0;
+#pragma unroll 8
+    for (int k = 0; k < wp; ++k) { off_m += s.sc_m[k]; off_c += s.sc_c[k]; }
+    inc_m += off_m; inc_c += off_c;
+    r.exc_m = inc_m - my_m; r.exc_c = inc_c - my_c;
+    if (tid == kSampThreads - 1) { s.tot_m = inc_m; s.tot_c = inc_c; }
+    __syncthreads();
+}
+
+// First non-empty level-0 bucket, from the highest down, at which the running mass reaches target: returns its
+// index (or -1 when the total stays below), the mass / count above it and its own.
+__device__ int l0_query(const L0Regs& r, SampScratch& s, unsigned long long target, unsigned long long& above_m,
+                        unsigned int& above_c, unsigned long long& bucket_mass, unsigned int& bucket_cnt) {
+    const int tid = threadIdx.x;
+    if (tid == 0) s.pick = kL0Buckets;
+    __syncthreads();
+    unsigned long long cum = r.exc_m; unsigned int cnt = r.exc_c;
+    int found = -1;
+#pragma unroll
+    for (int k = 0; k < kL0PerThread; ++k) {
+        if (found < 0) {
+            if (r.c[k] > 0 && cum + r.m[k] >= target) found = k;
+            else { cum += r.m[k]; cnt += r.c[k]; }
+        }
+    }
+    if (found >= 0) atomicMin(&s.pick, tid * kL0PerThread + found);
+    __syncthreads();
+    const int pick = s.pick;
+    if (pick == kL0Buckets) {
+        above_m = s.tot_m; above_c = s.tot_c;
+        __syncthreads();
+        return -1;
+    }
+    if (pick / kL0PerThread == tid) {
+        s.pk_above_m = cum; s.pk_above_c = cnt;
+#pragma unroll
+        for (int k = 0; k < kL0PerThread; ++k)
+            if (k == found) { s.pk_m = r.m[k]; s.pk_c = r.c[k]; }
+    }
+    __syncthreads();
+    above_m = s.pk_above_m; above_c = s.pk_above_c;
+    bucket_mass = s.pk_m; bucket_cnt = s.pk_c;
+    __syncthreads();
+    return kL0Buckets - 1 - pick;
+}
+
+// Finds the element, in descending (key, then ascending id) order, at which the running mass first reaches
+// `target`, inside the key range [lo, hi] of a level-0 bucket known to contain it; cum / cnt are the mass and count
+// above that bucket; h1 is working space.
+__device__ SelectResult select_mass(const float* w, int V, unsigned long long target, uint32_t lo, uint32_t hi,
+                                    unsigned long long cum, unsigned int cnt, SampHist& h1, SampScratch& s) {
+    const int tid = threadIdx.x;
+    unsigned long long bm = 0; unsigned int bc = 0;
     SelectResult res;
     res.found = 0; res.qk = 0; res.ties = 0; res.r = 0; res.key = 0;
-    uint32_t lo = 0, hi = 0;
-    int b = scan_pick(l0_m, l0_c, kSampBuckets - 1, s, target, cum, cnt, bm, bc);
-    if (b >= 0) {
-        l0_range(b, lo, hi);
-        for (int pass = 0; pass < 4; ++pass) {
-            const int sh = shift_for(hi - lo);
-            hist_clear(h1);
-            __syncthreads();
-            for (int i = tid; i < V; i += kSampThreads) {
-                const uint32_t key = __float_as_uint(w[i]);
-                if (key >= lo && key <= hi) hist_add(h1, (int)((key - lo) >> sh), fix_of(w[i]));
-            }
-            __syncthreads();
-            const int top = (int)((hi - lo) >> sh);
-            const int bb = top - tid;
-            b = scan_pick(bb >= 0 ? hist_mass(h1, bb) : 0ull, bb >= 0 ? h1.cnt[bb] : 0u, top, s, target, cum, cnt, bm, bc);
-            if (b < 0) break;                    // cannot happen: the parent bucket contained the crossing
-            const uint32_t nlo = lo + ((uint32_t)b << sh);
-            uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
-            if (nhi > hi) nhi = hi;
-            lo = nlo; hi = nhi;
-            if (sh == 0) {                       // one key per bucket: done
-                res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
-                const unsigned long long need = target > cum ? target - cum : 0;
-                unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
-                if (r < 1) r = 1;
-                if (r > bc) r = bc;
-                res.r = (unsigned int)r;
-                break;
-            }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int sh = shift_for(hi - lo);
+        hist_clear(h1);
+        __syncthreads();
+        for (int i = tid; i < V; i += kSampThreads) {
+            const uint32_t key = __float_as_uint(w[i]);
+            if (key >= lo && key <= hi) hist_add(h1, (int)((key - lo) >> sh), fix_of(w[i]));
+        }
+        __syncthreads();
+        const int top = (int)((hi - lo) >> sh);
+        const int bb = top - tid;
+        const int b = scan_pick(bb >= 0 ? hist_mass(h1, bb) : 0ull, bb >= 0 ? h1.cnt[bb] : 0u, top, s, target, cum, cnt, bm, bc);
+        if (b < 0) break;                        // cannot happen: the parent bucket contained the crossing
+        const uint32_t nlo = lo + ((uint32_t)b << sh);
+        uint32_t nhi = (sh == 0) ? nlo : (nlo + ((1u << sh) - 1u));
+        if (nhi > hi) nhi = hi;
+        lo = nlo; hi = nhi;
+        if (sh == 0) {                           // one key per bucket: done
+            res.found = 1; res.key = lo; res.ties = bc; res.qk = bm / bc;
+            const unsigned long long need = target > cum ? target - cum : 0;
+            unsigned long long r = res.qk ? (need + res.qk - 1) / res.qk : 1;
+            if (r < 1) r = 1;
+            if (r > bc) r = bc;
+            res.r = (unsigned int)r;
+            break;
         }
     }
     res.cum_above = cum; res.cnt_above = cnt;
@@ -301,20 +389,20 @@ __device__ int cand_solve(const float* w, int V, uint32_t lo, uint32_t hi, unsig
 // Where the descending running mass first reaches `target`: through the candidate solver when the level-0
 // bucket is small enough (the usual case), else through the histogram refinement.
 struct Loc { int found, have_id, id; unsigned long long mass_incl; unsigned int cnt_incl; uint32_t key; unsigned int r; };
-__device__ Loc locate(const float* w, int V, unsigned long long target, unsigned long long l0_m, unsigned int l0_c,
-                      SampHist& h1, SampScratch& sc, CandScratch& cs) {
+__device__ Loc locate(const float* w, int V, unsigned long long target, const L0Regs& l0, SampHist& h1, SampScratch& sc,
+                      CandScratch& cs) {
     Loc L; L.found = 0; L.have_id = 0; L.id = -1; L.key = 0; L.r = 0;
     unsigned long long cum = 0, bm = 0; unsigned int cnt = 0, bc = 0;
-    const int b = scan_pick(l0_m, l0_c, kSampBuckets - 1, sc, target, cum, cnt, bm, bc);
+    const int b = l0_query(l0, sc, target, cum, cnt, bm, bc);
     if (b < 0) { L.mass_incl = cum; L.cnt_incl = cnt; return L; }
+    uint32_t lo, hi;
+    l0_range(b, lo, hi);
     if (bc <= (unsigned int)kSampCand) {
-        uint32_t lo, hi;
-        l0_range(b, lo, hi);
         unsigned long long m = 0; unsigned int c = 0; int id = -1;
         const int pick = cand_solve(w, V, lo, hi, bc, target > cum ? target - cum : 0ull, cs, id, m, c);
         if (pick >= 0) { L.found = 1; L.have_id = 1; L.id = id; L.mass_incl = cum + m; L.cnt_incl = cnt + c; return L; }
     }
-    const SelectResult r = select_mass(w, V, target, l0_m, l0_c, h1, sc);
+    const SelectResult r = select_mass(w, V, target, lo, hi, cum, cnt, h1, sc);
     L.found = r.found; L.key = r.key; L.r = r.r;
     L.mass_incl = r.found ? r.cum_above + (unsigned long long)r.r * r.qk : r.cum_above;
     L.cnt_incl = r.found ? r.cnt_above + r.r : r.cnt_above;
@@ -381,18 +469,26 @@ __global__ void __launch_bounds__(kSampPartThreads) k_samp_hist(const SampleArgs
     pdl_wait();
     SLLM_TL(310);
     const int slot = blockIdx.y, tid = threadIdx.x;
+    const int per = (a.V + a.bps - 1) / a.bps, b0 = blockIdx.x * per, b1 = min(a.V, b0 + per);
+    const float* lg = a.logits + (size_t)slot * a.V;
+    const uint32_t* seen = a.st.seen + (size_t)slot * (a.V / 32);
+    // the thread's first element is requested before the maximum's reduction (with one block row per SM it is
+    // the only one), so the two round trips overlap
+    const int i0 = b0 + tid;
+    const float raw0 = i0 < b1 ? lg[i0] : 0.f;
+    const uint32_t word0 = i0 < b1 ? seen[i0 >> 5] : 0u;
     if (a.st.finished[slot]) return;
     float mx; int arg;
     slot_max(a, slot, &s_val, &s_idx, mx, arg);
     if (!isfinite(mx)) return;
-    const int per = (a.V + a.bps - 1) / a.bps, b0 = blockIdx.x * per, b1 = min(a.V, b0 + per);
-    const float* lg = a.logits + (size_t)slot * a.V;
-    const uint32_t* seen = a.st.seen + (size_t)slot * (a.V / 32);
     float* w = a.g_w + (size_t)slot * a.V;
-    unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
-    unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
-    for (int i = b0 + tid; i < b1; i += kSampPartThreads) {
-        const float e = expf((penalised(a, lg, seen, i) - mx) / a.temperature);
+    unsigned long long* gm = a.g_mass + (size_t)slot * kL0Buckets;
+    unsigned int* gc = a.g_cnt + (size_t)slot * kL0Buckets;
+    for (int i = i0; i < b1; i += kSampPartThreads) {
+        float sv = i == i0 ? raw0 : lg[i];
+        const uint32_t word = i == i0 ? word0 : seen[i >> 5];
+        if (a.penalty != 1.0f && ((word >> (i & 31)) & 1u)) sv = sv > 0.f ? sv / a.penalty : sv * a.penalty;
+        const float e = expf((sv - mx) / a.temperature);
         w[i] = e;
         const int b = l0_bucket(__float_as_uint(e));
         atomicAdd(gm + b, fix_of(e));              // results unused: reductions performed in L2
@@ -406,11 +502,9 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
     __shared__ SampHist h1;
     __shared__ SampScratch sc;
     __shared__ CandScratch cs;
-    __shared__ unsigned long long r_sum[32];
     __shared__ unsigned int s_scan[32];
     __shared__ int s_out;
     __shared__ float s_val; __shared__ int s_idx;
-    __shared__ unsigned long long s_total;
 
     const int slot = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int V = a.V;
@@ -418,60 +512,74 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
     pdl_wait();
 
     SLLM_TL(320);
+    // Everything the sampling path reads from global memory is requested up front, ahead of the maximum's reduction:
+    // the first trip of the weights and this thread's share of the level-0 histogram (which is cleared for the
+    // next step; a finished slot's histogram is empty and its weights are not used).
+    const bool sampling = a.temperature > 0.0f;
+    unsigned long long* gm = a.g_mass + (size_t)slot * kL0Buckets;
+    unsigned int* gc = a.g_cnt + (size_t)slot * kL0Buckets;
+    const float* gw = a.g_w + (size_t)slot * V;
+    float pv[4]; int pi[4];                                    // warp 0: the per-block maxima (bps <= 128)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int b = tid + 32 * k;
+        const bool in = tid < 32 && b < a.bps;
+        pv[k] = in ? __ldcg(a.g_pmax_val + (size_t)slot * a.bps + b) : -INFINITY;
+        pi[k] = in ? __ldcg(a.g_pmax_idx + (size_t)slot * a.bps + b) : 0x7fffffff;
+    }
     int n_tok = a.st.n_tok[slot];
     const int fin = a.st.finished[slot];
+    double u = 0.0;
+    if (sampling && a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
+    L0Regs l0;
+    if (sampling) {
+        l0_load(gm, gc, l0);
+        for (int base = 0; base < V; base += kSampThreads * 4 * 8) {          // 8 independent 16-byte loads per thread and trip
+            float4 t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + (j * kSampThreads + tid) * 4;
+                t[j] = i < V ? __ldcg(reinterpret_cast<const float4*>(gw + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + (j * kSampThreads + tid) * 4;
+                if (i < V) *reinterpret_cast<float4*>(w + i) = t[j];
+            }
+        }
+    }
+    // the slot's maximum (first index among equals) from the per-block maxima
+    if (tid < 32) {
+        float bv = pv[0]; int bi = pi[0];
+#pragma unroll
+        for (int k = 1; k < 4; ++k) first_max(bv, bi, pv[k], pi[k]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) first_max(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (tid == 0) { s_val = bv; s_idx = bi; }
+    }
+    __syncthreads();
+    const float mx = s_val; const int arg = s_idx;
     int token = -1;
     if (!fin) {
-        float mx; int arg;
-        slot_max(a, slot, &s_val, &s_idx, mx, arg);
         if (!isfinite(mx)) {
             if (tid == 0) a.st.finished[slot] = 3;
-        } else if (a.temperature <= 0.0f) {
+        } else if (!sampling) {
             token = arg;
         } else {
-            unsigned long long* gm = a.g_mass + (size_t)slot * kSampBuckets;
-            unsigned int* gc = a.g_cnt + (size_t)slot * kSampBuckets;
-            // this thread's level-0 bucket (descending order: thread 0 holds the bucket of weight 1.0)
-            const int b0 = kSampBuckets - 1 - tid;
-            const unsigned long long l0_m = __ldcg(gm + b0);
-            const unsigned int l0_c = __ldcg(gc + b0);
-            gm[b0] = 0ull; gc[b0] = 0u;                        // ready for the next step
-            const float* gw = a.g_w + (size_t)slot * V;
-            for (int base = 0; base < V; base += kSampThreads * 4 * 8) {      // 8 independent 16-byte loads per thread and trip
-                float4 t[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = base + (j * kSampThreads + tid) * 4;
-                    t[j] = i < V ? __ldcg(reinterpret_cast<const float4*>(gw + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = base + (j * kSampThreads + tid) * 4;
-                    if (i < V) *reinterpret_cast<float4*>(w + i) = t[j];
-                }
-            }
-            unsigned long long sum = l0_m;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) r_sum[wp] = sum;
-            __syncthreads();
-            if (tid == 0) { unsigned long long t = 0; for (int i = 0; i < 32; ++i) t += r_sum[i]; s_total = t; }
-            __syncthreads();
-            const unsigned long long total = s_total;
+            l0_scan(l0, sc);                                   // ends with a block barrier: w is complete too
+            const unsigned long long total = sc.tot_m;
             SLLM_TL(322);
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
-            const Loc cut = locate(w, V, t1, l0_m, l0_c, h1, sc, cs);
+            const Loc cut = locate(w, V, t1, l0, h1, sc, cs);
             const unsigned long long kept_mass = cut.mass_incl;
             const unsigned int kept = cut.cnt_incl;
             SLLM_TL(323);
             // ---- the draw -------------------------------------------------------------------------
-            double u = 0.0;
-            if (a.draws) u = a.draws[(size_t)slot * a.draws_stride + min(a.st.draw_idx[slot], a.draws_stride - 1)];
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
-            const Loc hit = locate(w, V, t2, l0_m, l0_c, h1, sc, cs);
+            const Loc hit = locate(w, V, t2, l0, h1, sc, cs);
             SLLM_TL(324);
             const Loc& use = (hit.found && hit.cnt_incl <= kept) ? hit : cut;    // else: the last kept candidate
             if (use.found) {
