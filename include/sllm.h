@@ -72,6 +72,8 @@ typedef struct {
     uint64_t launches;           /* kernels launched by this engine since creation (graph nodes counted per replay) */
     uint64_t decode_steps;
     float last_step_ms;          /* device time of the most recent sllm_decode_step         */
+    uint32_t reserved;
+    uint64_t prefill_tokens;     /* positions run through prefill passes (prompts, appended turns) */
 } sllm_stats;
 
 void sllm_default_model_config(sllm_model_config* cfg);      /* include/config.h:15-46 defaults */
@@ -157,6 +159,12 @@ int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt,
 /* Put a prompt (1..context_length ids) into one slot and run it through the model; other slots are untouched.
  * Slots below `slot` that were never assigned are parked (idle). */
 int sllm_slot_assign(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_t len);
+/* Append ids behind a live slot's tokens (a further turn of a conversation) and run only them through the model:
+ * the positions before them are served from the slot's KV pages.  The slot's stop state is cleared and its step
+ * logits are those of the last appended id.  No counterpart in the reference, whose chat loop re-encodes and
+ * re-runs each turn from position 0 (src/main.cpp:46-62); the history handling this serves is that of the
+ * browser demo (docs/script.js:288-305).  SLLM_ERR_CAPACITY when history + ids exceed context_length. */
+int sllm_slot_append(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_t len);
 /* Park a slot: its KV pages return to the pool, the sampler skips it. */
 int sllm_slot_release(sllm_engine* e, uint32_t slot);
 /* Finished flags of slots 0..n-1 to HOST memory: 0 live, 1 EOS / stop token / parked, 2 context full, 3 non-finite logits. */

@@ -163,7 +163,13 @@ public:
             throw std::invalid_argument("Model::forward: seq_len exceeds context_length");
         Tensor logits({batch_size, seq_len, config_.vocab_size});
         sllm_engine* e = engine();
-        sllm_detail::check(sllm_forward_logits(e, token_ids.data(), batch_size, seq_len, logits.data()), e);
+        // rows are independent: more rows than the engine has sequence slots go through in groups
+        const size_t group = options_.max_batch ? options_.max_batch : 1;
+        for (size_t b0 = 0; b0 < batch_size; b0 += group) {
+            const size_t nb = std::min(group, batch_size - b0);
+            sllm_detail::check(sllm_forward_logits(e, token_ids.data() + b0 * seq_len, nb, seq_len,
+                                                   logits.data() + b0 * seq_len * config_.vocab_size), e);
+        }
         return logits;
     }
 
@@ -436,4 +442,82 @@ public:
 private:
     Model& model_;
     Tokenizer& tokenizer_;
+};
+
+// Multi-turn chat on one engine slot with the KV cache carried across turns.  An extension: the reference's
+// chat loop (src/main.cpp:46-62) sends every line as a fresh single-turn prompt.  The history rules are those
+// of its browser demo (docs/script.js:288-305): a turn's context is the stored turns followed by
+// <|user|> text <|end|> <|assistant|>; a finished turn is stored as prompt + reply + <|end|>; when history,
+// prompt and reply budget no longer fit context_length, the history is dropped.  Only the new ids run
+// through the model (sllm_slot_append); draws come from std::mt19937_64(opt.seed), one per step.
+class ChatSession {
+public:
+    ChatSession(Model& model, Tokenizer& tokenizer, uint32_t slot = 0) : model_(model), tokenizer_(tokenizer), slot_(slot) {}
+
+    // reply ids without the token that ended the turn
+    std::vector<uint32_t> sayIds(const std::vector<uint32_t>& user_ids, size_t max_new_tokens, SamplingOptions opt = {}) {
+        const ChatTokens ids = chatTokens(tokenizer_);
+        const size_t ctx = model_.config().context_length;
+        std::vector<uint32_t> prompt;
+        prompt.push_back(ids.user);
+        prompt.insert(prompt.end(), user_ids.begin(), user_ids.end());
+        prompt.push_back(ids.end);
+        prompt.push_back(ids.assistant);
+        if (prompt.size() + max_new_tokens > ctx)
+            throw std::invalid_argument("ChatSession::say: prompt and reply budget exceed context_length");
+        sllm_engine* e = model_.engine();
+        const size_t held = started_ ? tokens(e).size() + (need_end_ ? 1 : 0) : 0;
+        if (!started_ || held + prompt.size() + max_new_tokens > ctx) {
+            if (started_) ++dropped_history_;
+            sllm_detail::check(sllm_slot_assign(e, slot_, prompt.data(), static_cast<uint32_t>(prompt.size())), e);
+            started_ = true;
+        } else {
+            std::vector<uint32_t> extra;
+            if (need_end_) extra.push_back(ids.end);
+            extra.insert(extra.end(), prompt.begin(), prompt.end());
+            sllm_detail::check(sllm_slot_append(e, slot_, extra.data(), static_cast<uint32_t>(extra.size())), e);
+        }
+        const size_t n_before = tokens(e).size();
+        sllm_sampling s;
+        s.temperature = opt.temperature; s.top_p = opt.top_p; s.repetition_penalty = opt.repetition_penalty;
+        s.eos_token = ids.eos; s.stop_token = ids.end; s.seed = opt.seed;
+        std::vector<double> draws;
+        if (opt.temperature > 0.0f) {                      // [step][slot], this slot's column filled
+            std::mt19937_64 rng(opt.seed + turns_);
+            draws.assign(max_new_tokens * (slot_ + 1), 0.0);
+            for (size_t i = 0; i < max_new_tokens; ++i) draws[i * (slot_ + 1) + slot_] = std::generate_canonical<double, 53>(rng);
+        }
+        sllm_detail::check(sllm_decode_loop(e, max_new_tokens, &s, draws.empty() ? nullptr : draws.data()), e);
+        ++turns_;
+        std::vector<uint32_t> all = tokens(e);
+        std::vector<uint32_t> reply(all.begin() + n_before, all.end());
+        if (!reply.empty() && reply.back() == ids.eos) {   // the demo drops EOS and closes the turn with <|end|>
+            sllm_detail::check(sllm_truncate(e, slot_, all.size() - 1), e);
+            reply.pop_back(); need_end_ = true;
+        } else if (!reply.empty() && reply.back() == ids.end) {
+            reply.pop_back(); need_end_ = false;
+        } else {
+            need_end_ = true;                              // budget exhausted
+        }
+        return reply;
+    }
+    std::string say(const std::string& user_text, size_t max_new_tokens, SamplingOptions opt = {}) {
+        return tokenizer_.decode(sayIds(tokenizer_.encode(user_text), max_new_tokens, opt));
+    }
+    size_t droppedHistory() const { return dropped_history_; }
+
+private:
+    std::vector<uint32_t> tokens(sllm_engine* e) {
+        std::vector<uint32_t> out(2 * model_.config().context_length + 2);
+        uint64_t n = 0;
+        sllm_detail::check(sllm_get_tokens(e, slot_, out.data(), out.size(), &n), e);
+        out.resize(n);
+        return out;
+    }
+    Model& model_;
+    Tokenizer& tokenizer_;
+    uint32_t slot_;
+    bool started_ = false, need_end_ = false;
+    size_t dropped_history_ = 0;
+    uint64_t turns_ = 0;
 };

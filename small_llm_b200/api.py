@@ -58,7 +58,8 @@ class _Sampling(C.Structure):
 class _Stats(C.Structure):
     _fields_ = [("weight_bytes", C.c_uint64), ("kv_bytes", C.c_uint64), ("scratch_bytes", C.c_uint64),
                 ("kv_pages_total", C.c_uint64), ("kv_pages_free", C.c_uint64), ("launches", C.c_uint64),
-                ("decode_steps", C.c_uint64), ("last_step_ms", C.c_float)]
+                ("decode_steps", C.c_uint64), ("last_step_ms", C.c_float), ("reserved", C.c_uint32),
+                ("prefill_tokens", C.c_uint64)]
 
 
 # every symbol include/sllm.h declares; tests check that the library exports all of them
@@ -68,7 +69,7 @@ ABI_SYMBOLS = [
     "sllm_param_info", "sllm_set_param", "sllm_load_checkpoint", "sllm_forward_logits", "sllm_reset",
     "sllm_prefill", "sllm_sample", "sllm_decode_step", "sllm_get_step_logits", "sllm_get_tokens",
     "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
-    "sllm_slot_assign", "sllm_slot_release", "sllm_get_finished",
+    "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished",
 ]
 
 
@@ -113,6 +114,7 @@ def load_library(path: str | None = None):
     lib.sllm_decode_loop.argtypes = [E, C.c_uint64, C.POINTER(_Sampling), f64p]
     i32p = C.POINTER(C.c_int32)
     lib.sllm_slot_assign.argtypes = [E, C.c_uint32, u32p, C.c_uint32]
+    lib.sllm_slot_append.argtypes = [E, C.c_uint32, u32p, C.c_uint32]
     lib.sllm_slot_release.argtypes = [E, C.c_uint32]
     lib.sllm_get_finished.argtypes = [E, i32p, C.c_uint32]
     for fn in (lib.sllm_k_attn_decode, lib.sllm_k_attn_decode_static):
@@ -317,6 +319,11 @@ class Engine:
     def slot_assign(self, slot: int, ids):
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
         self._ck(self.lib.sllm_slot_assign(self.h, slot, ids.ctypes.data_as(u32p), ids.size))
+
+    def slot_append(self, slot: int, ids):
+        """Appends ids behind a live slot's tokens; only they run through the model (KV reuse across turns)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        self._ck(self.lib.sllm_slot_append(self.h, slot, ids.ctypes.data_as(u32p), ids.size))
 
     def slot_release(self, slot: int):
         self._ck(self.lib.sllm_slot_release(self.h, slot))

@@ -135,7 +135,7 @@ struct sllm_engine {
     // graphs
     std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;   // exec + kernels per replay
 
-    uint64_t launches = 0, decode_steps = 0;
+    uint64_t launches = 0, decode_steps = 0, prefill_tokens = 0;
     int iter_launches = 0;             // kernels in the decode-iteration graph captured last
     float last_step_ms = 0.f;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -888,8 +888,9 @@ int check_status(sllm_engine* e) {
 
 // Runs every prompt position through the model in chunks.  want_all: logits of every position go
 // to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
+// pos0s: first position of each sequence's ids (tokens appended behind what the slot's KV cache already holds).
 int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits,
-                 const int* slot_ids = nullptr) {
+                 const int* slot_ids = nullptr, const int* pos0s = nullptr) {
     const ModelDims& m = e->md;
     std::vector<uint32_t> c_id; std::vector<int> c_slot, c_pos, c_row; std::vector<int> c_row_dst;
     std::vector<PfTile> c_tiles;
@@ -903,6 +904,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         CU(cudaMemcpyAsync(e->d_tok_pos, c_pos.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         CU(cudaMemcpyAsync(e->d_tiles, c_tiles.data(), c_tiles.size() * sizeof(PfTile), cudaMemcpyHostToDevice, e->stream));
         PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n, e->d_tiles, (int)c_tiles.size()};
+        e->prefill_tokens += (uint64_t)n;
         int rc = run_pass(e, pv, nullptr, 0, nullptr, false);
         if (rc) return rc;
         // logits rows of this chunk, in groups that fit the logits buffer
@@ -929,13 +931,14 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         for (uint32_t i = 0; i < lens[s]; ++i) {
             if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
             const int slot = slot_ids ? slot_ids[s] : (int)s;
+            const int pos = (pos0s ? pos0s[s] : 0) + (int)i;
             if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
             if (!c_tiles.empty() && c_tiles.back().slot == slot && c_tiles.back().n_q < kPfQ &&
-                c_tiles.back().pos0 + c_tiles.back().n_q == (int)i && c_tiles.back().tok_begin + c_tiles.back().n_q == (int)c_id.size())
+                c_tiles.back().pos0 + c_tiles.back().n_q == pos && c_tiles.back().tok_begin + c_tiles.back().n_q == (int)c_id.size())
                 c_tiles.back().n_q += 1;
             else
-                c_tiles.push_back(PfTile{(int)c_id.size(), 1, slot, (int)i});
-            c_id.push_back(ids[off + i]); c_slot.push_back(slot); c_pos.push_back((int)i);
+                c_tiles.push_back(PfTile{(int)c_id.size(), 1, slot, pos});
+            c_id.push_back(ids[off + i]); c_slot.push_back(slot); c_pos.push_back(pos);
         }
         off += lens[s];
     }
@@ -1183,6 +1186,7 @@ int sllm_engine_stats(sllm_engine* e, sllm_stats* s) {
     s->weight_bytes = e->weight_bytes; s->kv_bytes = e->kv_bytes; s->scratch_bytes = e->scratch_bytes;
     s->kv_pages_total = (uint64_t)e->n_pages - 1; s->kv_pages_free = e->free_pages.size();
     s->launches = e->launches; s->decode_steps = e->decode_steps; s->last_step_ms = e->last_step_ms;
+    s->reserved = 0; s->prefill_tokens = e->prefill_tokens;
     return SLLM_OK;
 }
 
@@ -1434,6 +1438,45 @@ int sllm_slot_assign(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_
     CU(cudaStreamSynchronize(e->stream));
     const int sl = (int)slot;
     return prefill_impl(e, ids, &len, 1, nullptr, &sl);
+}
+
+// Tokens appended behind a live slot's history: only the new ids (and the slot's last token, whose KV entry may
+// not exist yet when the loop ended on a sampling step) run through the model; earlier positions are served
+// from the slot's KV pages.
+int sllm_slot_append(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_t len) {
+    if (!e || !ids) return fail(e, SLLM_ERR_INVALID, "sllm_slot_append: null argument");
+    const ModelDims& m = e->md;
+    if (slot >= (uint32_t)e->n_live || e->slot_released[slot]) return fail(e, SLLM_ERR_STATE, "sllm_slot_append: slot holds no sequence");
+    if (len == 0) return fail(e, SLLM_ERR_INVALID, "sllm_slot_append: no tokens");
+    for (uint32_t i = 0; i < len; ++i)
+        if (ids[i] >= (uint32_t)m.V) return fail(e, SLLM_ERR_INVALID, "token id outside the vocabulary");
+    int nt = 0;
+    CU(cudaMemcpyAsync(&nt, e->st.n_tok + slot, 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    if (nt < 1) return fail(e, SLLM_ERR_STATE, "sllm_slot_append: empty slot");
+    if ((uint64_t)nt + len > (uint64_t)m.ctx) return fail(e, SLLM_ERR_CAPACITY, "sllm_slot_append: history plus new tokens exceed context_length");
+    const int cap = e->st.tok_cap, words = m.V / 32;
+    std::vector<uint32_t> run(len + 1), seen(words);
+    CU(cudaMemcpyAsync(run.data(), e->st.tokens + (size_t)slot * cap + (nt - 1), 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaMemcpyAsync(seen.data(), e->st.seen + (size_t)slot * words, (size_t)words * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    for (uint32_t i = 0; i < len; ++i) { run[i + 1] = ids[i]; seen[ids[i] >> 5] |= 1u << (ids[i] & 31); }
+    const int n = nt + (int)len, zero = 0;
+    bool changed = false;
+    e->h_len_bound[slot] = n;
+    int rc = ensure_pages(e, (int)slot, n, &changed);
+    if (rc) return rc;
+    rc = upload_block_table(e, (int)slot);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(e->st.tokens + (size_t)slot * cap + nt, ids, (size_t)len * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.seen + (size_t)slot * words, seen.data(), (size_t)words * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.n_tok + slot, &n, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.finished + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->st.draw_idx + slot, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    const int sl = (int)slot, pos0 = nt - 1;
+    const uint32_t run_len = len + 1;
+    return prefill_impl(e, run.data(), &run_len, 1, nullptr, &sl, &pos0);
 }
 
 int sllm_slot_release(sllm_engine* e, uint32_t slot) {

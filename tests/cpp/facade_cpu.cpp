@@ -12,6 +12,8 @@ int main() {
     if (model.parameters().size() != 20) return 4;
     Tokenizer tok; Inference inf(model, tok);
     try { inf.generateTokens({}, 3); return 5; } catch (const std::invalid_argument&) {}
+    ChatSession chat(model, tok);
+    try { chat.sayIds(std::vector<uint32_t>(80, 1u), 8); return 7; } catch (const std::invalid_argument&) {}   // does not fit 64 positions
     model.to(Device::CUDA);
     try { model.forward({1,2,3}, 1, 3); return 6; } catch (const std::runtime_error& e) { std::cout << e.what() << "\n"; }
     return 0;
