@@ -152,6 +152,13 @@ int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* pr
  * the stream is idle.  draws_dev_index selects how draws are consumed as in sllm_generate. */
 int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws);
 
+/* ops::cross_entropy(Model::forward(ids), targets, num_valid), src/ops/cross_entropy.cpp:14-54, without moving
+ * the logits off the device: the mean over the counted positions of -logit[target] + log-sum-exp, per-row terms in
+ * fp32, summed in double in row order.  targets[i] < 0 = position ignored (the reference's SFT mask); num_valid 0 =
+ * divide by B*T.  What a perplexity check of a trained checkpoint needs (exp(loss)).  Uses slots 0..B-1. */
+int sllm_eval_loss(sllm_engine* e, const uint32_t* ids, const int32_t* targets, uint64_t B, uint64_t T, uint64_t num_valid,
+                   float* loss);
+
 /* ---- single slots: continuous batching ------------------------------------------------------
  * No counterpart in the reference (it generates one sequence at a time); these keep a batched decode
  * loop full: when a slot stops (EOS, stop token, budget), the caller collects its tokens, releases it

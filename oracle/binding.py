@@ -122,6 +122,8 @@ def orc():
         lib.orc_prompt_ids.argtypes = [C.c_uint32, C.c_uint64, C.c_uint32, u32p]
         lib.orc_uniforms.argtypes = [C.c_uint32, C.c_uint64, f32p]
         lib.orc_canonical64.argtypes = [C.c_uint64, C.c_uint64, f64p]
+        lib.orc_cross_entropy.argtypes = [f32p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64]
+        lib.orc_cross_entropy.restype = C.c_float
         _orc = lib
     return _orc
 
@@ -138,6 +140,15 @@ def uniforms(seed: int, n: int) -> np.ndarray:
     out = np.empty(n, dtype=np.float32)
     orc().orc_uniforms(seed, n, _ptr(out, f32p))
     return out
+
+
+def cross_entropy(logits: np.ndarray, targets: np.ndarray, num_valid: int = 0) -> float:
+    """ops::cross_entropy restated: logits [n, V] fp32, targets [n] (negative = ignored position)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    V = logits.shape[-1]
+    targets = np.ascontiguousarray(targets, dtype=np.int32).reshape(-1)
+    assert logits.size == targets.size * V
+    return float(orc().orc_cross_entropy(_ptr(logits, f32p), targets.ctypes.data_as(C.POINTER(C.c_int32)), targets.size, V, num_valid))
 
 
 def canonical64(seed: int, n: int) -> np.ndarray:
@@ -305,6 +316,7 @@ class RefModel:
         lib.ref_op_rope.argtypes = [f32p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, f32p]
         lib.ref_op_attention.argtypes = [f32p, f32p, f32p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, f32p]
         lib.ref_op_silu_mul.argtypes = [f32p, f32p, C.c_uint64, f32p]
+        lib.ref_op_cross_entropy.argtypes = [f32p, f32p, C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(C.c_float)]
         self.lib = lib
         self.cfg = cfg
         c = cfg.as_u64()
@@ -354,6 +366,15 @@ class RefModel:
         out = np.empty((B, T, self.cfg.vocab), dtype=np.float32)
         self._check(self.lib.ref_model_forward(self.h, _ptr(ids, u32p), B, T, _ptr(out, f32p)))
         return out
+
+    def cross_entropy(self, logits: np.ndarray, targets: np.ndarray, num_valid: int = 0) -> float:
+        """The reference's ops::cross_entropy on host logits [n, V]; targets as it stores them (ids as floats)."""
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        V = logits.shape[-1]
+        t = np.ascontiguousarray(targets, dtype=np.float32).reshape(-1)
+        out = C.c_float()
+        self._check(self.lib.ref_op_cross_entropy(_ptr(logits, f32p), _ptr(t, f32p), t.size, V, num_valid, C.byref(out)))
+        return float(out.value)
 
     def generate_tokens(self, prompt, max_new, temperature, top_p, penalty, seed, stop=-1,
                         eos_merges=32506) -> np.ndarray:

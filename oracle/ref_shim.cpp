@@ -15,6 +15,7 @@
 #include "inference.h"
 #include "model.h"
 #include "ops/attention.h"
+#include "ops/cross_entropy.h"
 #include "ops/elementwise.h"
 #include "ops/embedding.h"
 #include "ops/matmul.h"
@@ -176,6 +177,11 @@ int ref_op_attention(const float* q, const float* k, const float* v,
 int ref_op_silu_mul(const float* g, const float* u, uint64_t n, float* y) {
     try { Tensor r = ops::multiply(ops::silu(wrap(g, {n})), wrap(u, {n}));
           std::memcpy(y, r.data(), n * 4); return 0; }
+    catch (const std::exception& e) { return fail(e, 6); }
+}
+// ops::cross_entropy on host logits; targets are ids stored as floats, negative = ignored position
+int ref_op_cross_entropy(const float* logits, const float* targets, uint64_t n, uint64_t V, uint64_t num_valid, float* loss) {
+    try { *loss = ops::cross_entropy(wrap(logits, {n, V}), wrap(targets, {n}), num_valid); return 0; }
     catch (const std::exception& e) { return fail(e, 6); }
 }
 

@@ -599,3 +599,21 @@ int orc_generate_seeded(orc_model* m, const uint32_t* prompt, uint64_t np, uint6
     free(d);
     return rc;
 }
+
+/* src/ops/cross_entropy.cpp:27-53: per counted row the fp32 maximum, the fp32 sequential sum of expf(l - max),
+ * loss = -l[target] + (max + logf(sum)); rows are added in double and divided in double. */
+float orc_cross_entropy(const float* logits, const int32_t* targets, uint64_t n, uint64_t V, uint64_t num_valid) {
+    double total = 0.0;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (targets[i] < 0) continue;
+        const float* l = logits + i * V;
+        float mx = l[0];
+        for (uint64_t j = 0; j < V; ++j) mx = l[j] > mx ? l[j] : mx;
+        float sum = 0.0f;
+        for (uint64_t j = 0; j < V; ++j) sum += expf(l[j] - mx);
+        const float lse = mx + logf(sum);
+        const float loss = -l[targets[i]] + lse;
+        total += loss;
+    }
+    return (float)(total / (double)(num_valid ? num_valid : n));
+}

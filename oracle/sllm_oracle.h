@@ -95,6 +95,10 @@ void orc_uniforms(uint32_t seed, uint64_t n, float* out);
 /* generate_canonical<double,53>(mt19937_64(seed)) stream: what discrete_distribution consumes. */
 void orc_canonical64(uint64_t seed, uint64_t n, double* out);
 
+/* ops::cross_entropy (src/ops/cross_entropy.cpp:14-54): mean over the counted positions of
+ * -logit[target] + max + log(sum exp(logit - max)); target < 0 = ignored; num_valid 0 = all n positions. */
+float orc_cross_entropy(const float* logits, const int32_t* targets, uint64_t n, uint64_t V, uint64_t num_valid);
+
 #ifdef __cplusplus
 }
 #endif

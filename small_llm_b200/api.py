@@ -69,7 +69,7 @@ ABI_SYMBOLS = [
     "sllm_param_info", "sllm_set_param", "sllm_load_checkpoint", "sllm_forward_logits", "sllm_reset",
     "sllm_prefill", "sllm_sample", "sllm_decode_step", "sllm_get_step_logits", "sllm_get_tokens",
     "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
-    "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished",
+    "sllm_eval_loss", "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished",
 ]
 
 
@@ -115,6 +115,7 @@ def load_library(path: str | None = None):
     i32p = C.POINTER(C.c_int32)
     lib.sllm_slot_assign.argtypes = [E, C.c_uint32, u32p, C.c_uint32]
     lib.sllm_slot_append.argtypes = [E, C.c_uint32, u32p, C.c_uint32]
+    lib.sllm_eval_loss.argtypes = [E, u32p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(C.c_float)]
     lib.sllm_slot_release.argtypes = [E, C.c_uint32]
     lib.sllm_get_finished.argtypes = [E, i32p, C.c_uint32]
     for fn in (lib.sllm_k_attn_decode, lib.sllm_k_attn_decode_static):
@@ -319,6 +320,16 @@ class Engine:
     def slot_assign(self, slot: int, ids):
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
         self._ck(self.lib.sllm_slot_assign(self.h, slot, ids.ctypes.data_as(u32p), ids.size))
+
+    def eval_loss(self, ids, targets, B: int, T: int, num_valid: int = 0) -> float:
+        """ops::cross_entropy of the model's logits against targets [B*T] (negative = ignored), computed on the device."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32).reshape(-1)
+        targets = np.ascontiguousarray(targets, dtype=np.int32).reshape(-1)
+        assert ids.size == B * T == targets.size
+        out = C.c_float()
+        self._ck(self.lib.sllm_eval_loss(self.h, ids.ctypes.data_as(u32p), targets.ctypes.data_as(C.POINTER(C.c_int32)),
+                                         B, T, num_valid, C.byref(out)))
+        return float(out.value)
 
     def slot_append(self, slot: int, ids):
         """Appends ids behind a live slot's tokens; only they run through the model (KV reuse across turns)."""

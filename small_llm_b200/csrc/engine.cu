@@ -102,6 +102,7 @@ struct sllm_engine {
     std::vector<int> h_attn_order;
     float* x = nullptr; float* q = nullptr; float* att = nullptr; float* hid = nullptr;
     int* d_row_tok = nullptr;
+    int* d_row_target = nullptr; float* d_row_loss = nullptr;    // sllm_eval_loss: targets and losses of one group of logits rows
     PfTile* d_tiles = nullptr;
     float* step_logits = nullptr;      // [max_batch][V]
     float* pass_logits = nullptr;      // [logit_rows_cap][V]
@@ -813,6 +814,36 @@ int set_param_impl(sllm_engine* e, int idx, const float* host) {
     return SLLM_OK;
 }
 
+// Teacher-forced loss of one logits row (ops::cross_entropy, src/ops/cross_entropy.cpp:27-50):
+// -logit[target] + max + log(sum exp(logit - max)) in fp32; rows with a negative target give 0.
+__global__ void __launch_bounds__(256) k_row_loss(const float* __restrict__ logits, const int* __restrict__ targets,
+                                                  float* __restrict__ loss, int V) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int tgt = targets[r];
+    if (tgt < 0) { if (tid == 0) loss[r] = 0.f; return; }
+    const float* l = logits + (size_t)r * V;
+    float mx = -INFINITY;
+    for (int j = tid; j < V; j += 256) mx = fmaxf(mx, l[j]);
+    mx = warp_max(mx);
+    if (lane == 0) red[wp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int j = tid; j < V; j += 256) sum += expf(l[j] - mx);
+    sum = warp_sum(sum);
+    if (lane == 0) red[wp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        loss[r] = -l[tgt] + (mx + logf(t));
+    }
+}
+
 int load_slots(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, bool allow_long = false) {
     const ModelDims& m = e->md;
     if (n_seq == 0 || n_seq > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_CAPACITY, "n_seq exceeds max_batch");
@@ -889,8 +920,10 @@ int check_status(sllm_engine* e) {
 // Runs every prompt position through the model in chunks.  want_all: logits of every position go
 // to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
 // pos0s: first position of each sequence's ids (tokens appended behind what the slot's KV cache already holds).
+// h_targets / h_row_loss: instead of logits, every position's teacher-forced loss against its target goes to the host.
 int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, float* host_logits,
-                 const int* slot_ids = nullptr, const int* pos0s = nullptr) {
+                 const int* slot_ids = nullptr, const int* pos0s = nullptr, const int32_t* h_targets = nullptr,
+                 float* h_row_loss = nullptr) {
     const ModelDims& m = e->md;
     std::vector<uint32_t> c_id; std::vector<int> c_slot, c_pos, c_row; std::vector<int> c_row_dst;
     std::vector<PfTile> c_tiles;
@@ -913,7 +946,13 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
             CU(cudaMemcpyAsync(e->d_row_tok, c_row.data() + r0, nr * 4, cudaMemcpyHostToDevice, e->stream));
             rc = run_head(e, pv, e->d_row_tok, nr, e->pass_logits);
             if (rc) return rc;
-            if (host_logits) {
+            if (h_targets) {
+                CU(cudaMemcpyAsync(e->d_row_target, h_targets + row_base + r0, (size_t)nr * 4, cudaMemcpyHostToDevice, e->stream));
+                k_row_loss<<<nr, 256, 0, e->stream>>>(e->pass_logits, e->d_row_target, e->d_row_loss, m.V);
+                CU(cudaGetLastError());
+                e->launches += 1;
+                CU(cudaMemcpyAsync(h_row_loss + row_base + r0, e->d_row_loss, (size_t)nr * 4, cudaMemcpyDeviceToHost, e->stream));
+            } else if (host_logits) {
                 CU(cudaMemcpyAsync(host_logits + (row_base + r0) * m.V, e->pass_logits, (size_t)nr * m.V * 4,
                                    cudaMemcpyDeviceToHost, e->stream));
             } else {
@@ -932,7 +971,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
             if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
             const int slot = slot_ids ? slot_ids[s] : (int)s;
             const int pos = (pos0s ? pos0s[s] : 0) + (int)i;
-            if (host_logits || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
+            if (host_logits || h_targets || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
             if (!c_tiles.empty() && c_tiles.back().slot == slot && c_tiles.back().n_q < kPfQ &&
                 c_tiles.back().pos0 + c_tiles.back().n_q == pos && c_tiles.back().tok_begin + c_tiles.back().n_q == (int)c_id.size())
                 c_tiles.back().n_q += 1;
@@ -1108,6 +1147,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->d_attn_order, e->max_batch, &e->scratch_bytes);
     A(&e->d_dec_pos, e->max_batch, &e->scratch_bytes);
     A(&e->d_row_tok, e->pass_cap, &e->scratch_bytes);
+    A(&e->d_row_target, e->logit_rows_cap, &e->scratch_bytes); A(&e->d_row_loss, e->logit_rows_cap, &e->scratch_bytes);
     A(&e->d_tiles, e->pass_cap, &e->scratch_bytes);
     A(&e->x, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->q, (size_t)e->pass_cap * D, &e->scratch_bytes);
     A(&e->att, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->hid, (size_t)e->pass_cap * F, &e->scratch_bytes);
@@ -1274,6 +1314,29 @@ int sllm_forward_logits(sllm_engine* e, const uint32_t* ids, uint64_t B, uint64_
         rc = prefill_impl(e, ids + b0 * T, lens.data(), nb, host_logits + b0 * T * e->md.V);
         if (rc) return rc;
     }
+    return SLLM_OK;
+}
+
+int sllm_eval_loss(sllm_engine* e, const uint32_t* ids, const int32_t* targets, uint64_t B, uint64_t T, uint64_t num_valid,
+                   float* loss) {
+    if (!e || !ids || !targets || !loss) return fail(e, SLLM_ERR_INVALID, "sllm_eval_loss: null argument");
+    if (B == 0 || T == 0) return fail(e, SLLM_ERR_INVALID, "sllm_eval_loss: empty batch");
+    if (T > (uint64_t)e->md.ctx) return fail(e, SLLM_ERR_INVALID, "Model::forward: seq_len exceeds context_length");
+    for (uint64_t i = 0; i < B * T; ++i)
+        if (targets[i] >= e->md.V) return fail(e, SLLM_ERR_INVALID, "sllm_eval_loss: target outside the vocabulary");
+    std::vector<float> row_loss(B * T, 0.f);
+    for (uint64_t b0 = 0; b0 < B; b0 += e->max_batch) {
+        const uint32_t nb = (uint32_t)std::min<uint64_t>(e->max_batch, B - b0);
+        std::vector<uint32_t> lens(nb, (uint32_t)T);
+        int rc = load_slots(e, ids + b0 * T, lens.data(), nb);
+        if (rc) return rc;
+        rc = prefill_impl(e, ids + b0 * T, lens.data(), nb, nullptr, nullptr, nullptr, targets + b0 * T, row_loss.data() + b0 * T);
+        if (rc) return rc;
+    }
+    double total = 0.0;                                   // rows added in order, in double, as the reference does
+    for (uint64_t i = 0; i < B * T; ++i)
+        if (targets[i] >= 0) total += row_loss[i];
+    *loss = (float)(total / (double)(num_valid ? num_valid : B * T));
     return SLLM_OK;
 }
 

@@ -62,9 +62,25 @@ def c1_probe():
                         last_param_sha=np.array(sha(r.param(r.num_params() - 2)[1])))
 
 
+def cross_entropy_vectors():
+    """ops::cross_entropy of the small model's own logits (next-token targets) and of a masked variant."""
+    r = RefModel(SMALL)
+    r.init_normal(3, 0.2)
+    ids = prompt_ids(1, 2 * 24, SMALL.vocab)
+    logits = r.forward(ids, 2, 24).reshape(48, SMALL.vocab)
+    targets = np.roll(ids.reshape(2, 24), -1, axis=1).reshape(-1).astype(np.int32)     # next id, wrapping inside a row
+    masked = targets.copy()
+    masked[::4] = -1
+    nv = int((masked >= 0).sum())
+    np.savez_compressed(os.path.join(OUT, "ce_ref.npz"), ids=ids, targets=targets, masked=masked,
+                        loss_all=np.float32(r.cross_entropy(logits, targets)),
+                        loss_masked=np.float32(r.cross_entropy(logits, masked, nv)))
+
+
 if __name__ == "__main__":
     if build_ref() is None:
         sys.exit("reference tree not available; golden vectors can only be regenerated where it is")
     small()
     c1_probe()
+    cross_entropy_vectors()
     print("golden vectors written to", OUT)

@@ -301,3 +301,27 @@ def test_config3_batch64_subset_against_oracle():
                 flips.append((s, i, margin))
     assert all(m < 1e-2 for _, _, m in flips), flips
     assert len(flips) <= 6, flips
+
+
+@pytest.mark.parametrize("fp32", [True, False])
+def test_eval_loss_matches_reference_cross_entropy(fp32, golden_dir):
+    """sllm_eval_loss against the reference's own ops::cross_entropy values (tests/golden/ce_ref.npz, produced by
+    the unmodified reference for these weights, ids and targets) and against the oracle on a ragged group count."""
+    import os
+    from oracle.binding import cross_entropy
+    g = np.load(os.path.join(golden_dir, "ce_ref.npz"))
+    o, eng = make_pair(SMALL, seed=3, stddev=0.2 if fp32 else 0.05, fp32=fp32, max_batch=2, via_checkpoint=False)
+    tol = 2e-5 if fp32 else 2e-2
+    nv = int((g["masked"] >= 0).sum())
+    if fp32:                                                # the golden values belong to the stddev-0.2 weights
+        assert abs(eng.eval_loss(g["ids"], g["targets"], 2, 24) - float(g["loss_all"])) <= tol
+        assert abs(eng.eval_loss(g["ids"], g["masked"], 2, 24, nv) - float(g["loss_masked"])) <= tol
+    # three rows on an engine with two slots: the third goes through in a second group
+    ids = prompt_ids(9, 3 * 40, SMALL.vocab)
+    targets = np.roll(ids.reshape(3, 40), -1, axis=1).reshape(-1).astype(np.int32)
+    targets[5::7] = -1
+    n = int((targets >= 0).sum())
+    ref = cross_entropy(o.forward(ids, 3, 40).reshape(120, SMALL.vocab), targets, n)
+    assert abs(eng.eval_loss(ids, targets, 3, 40, n) - ref) <= tol
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.eval_loss(ids, np.full(120, SMALL.vocab, np.int32), 3, 40)

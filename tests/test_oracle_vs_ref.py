@@ -96,3 +96,23 @@ def test_reference_greedy_quirk():
     r.init_normal(3, 0.2)
     prompt = prompt_ids(1, 6, cfg.vocab)
     assert np.array_equal(r.generate_tokens(prompt, 5, 0.0, 0.9, 1.0, 1, eos_merges=250), prompt)
+
+
+def test_cross_entropy_bit_equal():
+    """ops::cross_entropy (src/ops/cross_entropy.cpp:14-54): all positions, masked positions with num_valid,
+    a single row, peaked and flat rows."""
+    from oracle.binding import cross_entropy
+    cfg = CFGS[0]
+    r = RefModel(cfg)
+    rng = np.random.default_rng(3)
+    logits = (rng.normal(0, 3.0, size=(37, cfg.vocab))).astype(np.float32)
+    logits[5] = 0.0
+    logits[6, 17] = 60.0
+    targets = rng.integers(0, cfg.vocab, size=37).astype(np.int32)
+    a, b = cross_entropy(logits, targets), r.cross_entropy(logits, targets)
+    assert np.float32(a) == np.float32(b)
+    masked = targets.copy()
+    masked[::3] = -1
+    nv = int((masked >= 0).sum())
+    assert np.float32(cross_entropy(logits, masked, nv)) == np.float32(r.cross_entropy(logits, masked, nv))
+    assert np.float32(cross_entropy(logits[:1], targets[:1])) == np.float32(r.cross_entropy(logits[:1], targets[:1]))
