@@ -124,13 +124,6 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
     for (int i = tid; i < n_pages && i < kTableCache; i += kStreamThreads) s_table[i] = table[i];
     __syncthreads();
 
-#ifdef SLLM_TIMELINE
-    unsigned long long tl_loc[40]; int tl_n = 0;
-#define TL_LOC() do { if (tl_n < 40) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); tl_loc[tl_n++] = t_; } } while (0)
-#else
-#define TL_LOC()
-#endif
-    TL_LOC();
     const int wk0 = warp * KW;                                    // this warp's first key inside a page
     // the last page may hold fewer keys than this warp's offset: then the warp has one page less
     const int last_nk = n_pages > 0 ? min(kPage, pos + 1 - (pg0 + n_pages - 1) * kPage) : 0;
@@ -162,7 +155,6 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         ok = bar_wait(as_smem(&bars[warp][s]), (pg / ST) & 1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        TL_LOC();
         const KVT* Kp = reinterpret_cast<const KVT*>(my_smem + (size_t)s * 2 * WBLK);
         const KVT* Vp = reinterpret_cast<const KVT*>(my_smem + (size_t)s * 2 * WBLK + WBLK);
         const int nkw = pos + 1 - (pg0 + pg) * kPage - wk0;     // valid keys among this warp's KW (>= 1)
@@ -220,7 +212,6 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         __syncwarp();                                            // every lane is done with stage s
         if (lane == 0 && pg + ST < my_pages) issue(pg + ST);
     }
-    TL_LOC();
     if (!ok) { s_ok = 0; atomicExch(status, 21u); }
     // merge the four warps' states
 #pragma unroll
@@ -239,14 +230,6 @@ __global__ void __launch_bounds__(kStreamThreads) k_attn_stream(const AttnDecArg
         for (int i = 0; i < 32; ++i) __nanosleep(16384);
         return;
     }
-    TL_LOC();
-#ifdef SLLM_TIMELINE
-    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        const unsigned int i0 = atomicAdd(&g_tl_n, (unsigned int)tl_n);
-        for (int i = 0; i < tl_n; ++i)
-            if (i0 + i < (1u << 15)) { g_tl_buf[2 * (i0 + i)] = 610 + i; g_tl_buf[2 * (i0 + i) + 1] = tl_loc[i]; }
-    }
-#endif
     float blk_m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) blk_m = fmaxf(blk_m, red_m[w]);

@@ -71,9 +71,20 @@ __device__ __forceinline__ void tl_stamp(unsigned int id) {
         if (i < (1u << 15)) { g_tl_buf[2 * i] = id; g_tl_buf[2 * i + 1] = t; }
     }
 }
+// stamp from whichever thread calls it (block 0 only): for single-thread roles such as an MMA issuer
+__device__ __forceinline__ void tl_stamp_here(unsigned int id) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const unsigned int i = atomicAdd(&g_tl_n, 1u);
+        if (i < (1u << 15)) { g_tl_buf[2 * i] = id; g_tl_buf[2 * i + 1] = t; }
+    }
+}
 #define SLLM_TL(id) tl_stamp(id)
+#define SLLM_TL_HERE(id) tl_stamp_here(id)
 #else
 #define SLLM_TL(id)
+#define SLLM_TL_HERE(id)
 #endif
 
 // ---- device-side view of the model and of the running sequences ----------------------------

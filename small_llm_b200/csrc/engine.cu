@@ -102,6 +102,7 @@ struct sllm_engine {
     std::vector<int> h_attn_order;
     float* x = nullptr; float* q = nullptr; float* att = nullptr; float* hid = nullptr;
     int* d_row_tok = nullptr;
+    float* ss_part = nullptr; int ss_parts = 0;    // folded RMSNorm: [pass_cap][ss_parts] partial sums of squares
     int* d_row_target = nullptr; float* d_row_loss = nullptr;    // sllm_eval_loss: targets and losses of one group of logits rows
     PfTile* d_tiles = nullptr;
     float* step_logits = nullptr;      // [max_batch][V]
@@ -413,9 +414,16 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
     for (int l = 0; l < m.L; ++l) {
         const LayerW& w = e->layers[l];
         a.layer = l;
-        int rc = launch(e, k_rmsnorm_bf16, dim3(n), dim3(256), 0, pdl, (const float*)e->x, w.g_attn, e->xn16, m.D, m.eps,
-                        (const int*)nullptr, l == 0 ? (const float*)e->emb_f32 : (const float*)nullptr, pv.tok_id, e->x);
-        if (rc) return rc;
+        // RMSNorm is folded into the projections (TcArgs): only the first layer needs a kernel of its own, which
+        // also gathers the embedding rows
+        int rc = SLLM_OK;
+        if (l == 0) {
+            rc = launch(e, k_embed_prep, dim3(n), dim3(256), 0, pdl, (const float*)e->emb_f32, pv.tok_id, w.g_attn, e->x, e->xn16,
+                        e->ss_part, m.D, e->ss_parts);
+            if (rc) return rc;
+        }
+        a.ss_in = e->ss_part; a.n_parts = e->ss_parts; a.eps = m.eps;
+        a.gain_next = nullptr; a.xn_out = nullptr; a.ss_out = nullptr;
         a.R = 3 * m.D; a.K = m.D; a.out = e->q; a.out_bf16 = nullptr;
         rc = launch_tc<kModeQKV>(e, e->map_wqkv[l], e->xn16, e->pass_cap, a, pdl);
         if (rc) return rc;
@@ -436,15 +444,16 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
         rc = launch_attn_any(e, t, pdl);
         if (rc) return rc;
         a.R = m.D; a.K = m.D; a.out = e->x;
+        a.ss_in = nullptr; a.gain_next = w.g_ffn; a.xn_out = e->xn16; a.ss_out = e->ss_part;
         rc = launch_tc<kModeResidual>(e, e->map_wo[l], e->att16, e->pass_cap, a, pdl);
         if (rc) return rc;
-        rc = launch(e, k_rmsnorm_bf16, dim3(n), dim3(256), 0, pdl, (const float*)e->x, w.g_ffn, e->xn16, m.D, m.eps,
-                    (const int*)nullptr, (const float*)nullptr, pv.tok_id, e->x);
-        if (rc) return rc;
+        a.ss_in = e->ss_part; a.gain_next = nullptr; a.xn_out = nullptr; a.ss_out = nullptr;
         a.R = 2 * m.F; a.K = m.D; a.out = nullptr; a.out_bf16 = e->hid16;
         rc = launch_tc<kModeGateUp>(e, e->map_wgu[l], e->xn16, e->pass_cap, a, pdl);
         if (rc) return rc;
         a.R = m.D; a.K = m.F; a.out = e->x; a.out_bf16 = nullptr;
+        a.ss_in = nullptr;
+        if (l + 1 < m.L) { a.gain_next = e->layers[l + 1].g_attn; a.xn_out = e->xn16; a.ss_out = e->ss_part; }
         rc = launch_tc<kModeResidual>(e, e->map_wd[l], e->hid16, e->pass_cap, a, pdl);
         if (rc) return rc;
     }
@@ -1176,6 +1185,8 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->d_status, 4, &e->scratch_bytes);
     if (!e->f32) {
         A(&e->xn16, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->att16, (size_t)e->pass_cap * D, &e->scratch_bytes);
+        e->ss_parts = 4 * (int)((D + kTcBM - 1) / kTcBM);
+        A(&e->ss_part, (size_t)e->pass_cap * e->ss_parts, &e->scratch_bytes);
         A(&e->hid16, (size_t)e->pass_cap * F, &e->scratch_bytes); A(&e->head16, (size_t)e->logit_rows_cap * D, &e->scratch_bytes);
         cudaDriverEntryPointQueryResult qres;
         if (!rc && (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &e->encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||

@@ -34,7 +34,33 @@ struct TcArgs {
     int layer;
     const float2* rope;
     unsigned int* status;           // engine status word (0 = fine)
+    // RMSNorm folded into the projections around it (src/ops/rmsnorm.cpp:38-60: y = x * r * g, r = 1/sqrt(mean(x^2) + eps)):
+    // a Residual epilogue that knows the next norm's gain stores bf16(x_new * g) as the next projection's operand and
+    // the sums of squares of its 32-row slices; the consuming epilogue multiplies its accumulator by r (the product is
+    // linear in r), which it gets from those partial sums.
+    const float* gain_next;         // Residual: gain of the norm that follows (null: nothing follows)
+    __nv_bfloat16* xn_out;          // Residual: [tok][R] bf16(x_new * gain_next)
+    float* ss_out;                  // Residual: [tok][n_parts] partial sums of squares, part = row tile * 4 + lane quarter
+    const float* ss_in;             // QKV / GateUp: the same array, written by the producer (null: operand already normalised)
+    int n_parts;
+    float eps;
 };
+
+// Sums v[j] over the 32 lanes for every j at once: afterwards lane j holds the sum of all lanes' v[j] (31 shuffles,
+// a fixed tree, so the result does not depend on timing).
+__device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+    for (int step = 16; step >= 1; step >>= 1) {
+        const bool up = (lane & step) != 0;
+#pragma unroll
+        for (int i = 0; i < step; ++i) {
+            const float send = up ? v[i] : v[i + step];
+            const float keep = up ? v[i + step] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+        }
+    }
+    return v[0];
+}
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,13 +210,8 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, a.status, 12);
                 if (!ok) break;
                 tc_fence_after();
-#ifdef SLLM_TIMELINE
-                if (kb == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-                    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-                    const unsigned int i = atomicAdd(&g_tl_n, 1u);
-                    if (i < (1u << 15)) { g_tl_buf[2 * i] = 502 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
-                }
-#endif
+                if (kb == 0) SLLM_TL_HERE(502 + MODE * 10);
+                if (kb == nkb - 1) SLLM_TL_HERE(505 + MODE * 10);
                 const uint32_t aaddr = smem_u32(sA + s * A_BYTES), baddr = smem_u32(sB + s * B_BYTES);
 #pragma unroll
                 for (int k = 0; k < kTcBK / 16; ++k)
@@ -230,7 +251,17 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         }
         float2 cs[MODE == kModeQKV ? CW : 1];
         float xv[MODE == kModeResidual ? CW : 1];
+        float rs = 1.0f;                                         // lane j: 1/rms of token column c + j (consumers of a folded norm)
+        const bool scaled = (MODE == kModeQKV || MODE == kModeGateUp) && a.ss_in != nullptr;
+        const float gnext = (MODE == kModeResidual && a.gain_next && row_ok) ? a.gain_next[row] : 0.f;
         auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
+            if (scaled) {
+                const int tok = t0 + c + lane;
+                float ss = 0.f;
+                if (lane < CW && tok < a.n_tok)
+                    for (int p = 0; p < a.n_parts; ++p) ss += a.ss_in[(size_t)tok * a.n_parts + p];
+                rs = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+            }
             if (MODE == kModeQKV) {
 #pragma unroll
                 for (int j = 0; j < CW; ++j)
@@ -247,13 +278,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         ok = mbar_wait(done_bar, 0, a.status, 13);
         ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
         tc_fence_after();
-#ifdef SLLM_TIMELINE
-        if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-            unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            const unsigned int i = atomicAdd(&g_tl_n, 1u);
-            if (i < (1u << 15)) { g_tl_buf[2 * i] = 503 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
-        }
-#endif
+        if (warp == 2 && lane == 0) SLLM_TL_HERE(503 + MODE * 10);
         for (int c0 = cbeg; c0 < cbeg + HALF && ok; c0 += CW) {
             if (t0 + c0 >= a.n_tok) break;                       // uniform over the warp
             const bool more = c0 + CW < cbeg + HALF && t0 + c0 + CW < a.n_tok;
@@ -267,7 +292,18 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c0 + j;
-                    if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = r[j];
+                    if (row_ok && tok < a.n_tok) {
+                        a.out[(size_t)tok * a.R + row] = r[j];
+                        if (a.gain_next) a.xn_out[(size_t)tok * a.R + row] = __float2bfloat16_rn(r[j] * gnext);
+                    }
+                }
+                if (a.gain_next) {                               // uniform over the grid
+                    float sq[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sq[j] = (j < CW && row_ok && t0 + c0 + j < a.n_tok) ? r[j < CW ? j : 0] * r[j < CW ? j : 0] : 0.f;
+                    const float col = warp_column_sums(sq, lane);
+                    const int tok = t0 + c0 + lane;
+                    if (lane < CW && tok < a.n_tok) a.ss_out[(size_t)tok * a.n_parts + blockIdx.x * 4 + quarter] = col;
                 }
             } else if (MODE == kModeHead) {
 #pragma unroll
@@ -281,18 +317,19 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 const bool store_lane = row_ok && (row & 1) == 0;
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]);
+                    const float acc = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs, j);
                     const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
                     const float hval = __fdividef(acc, 1.0f + __expf(-acc)) * other;
                     const int tok = t0 + c0 + j;
                     if (store_lane && tok < a.n_tok) a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn(hval);
                 }
+                if (more) fetch(c0 + CW);
             } else {
                 // RoPE pairs sit in adjacent lanes
                 float r[CW];
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]);
+                    const float acc = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs, j);
                     const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
                     r[j] = acc;
                     if (which < 2) r[j] = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
@@ -313,13 +350,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
             }
         }
     }
-#ifdef SLLM_TIMELINE
-    if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-        unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        const unsigned int i = atomicAdd(&g_tl_n, 1u);
-        if (i < (1u << 15)) { g_tl_buf[2 * i] = 504 + MODE * 10; g_tl_buf[2 * i + 1] = t; }
-    }
-#endif
+    if (warp == 2 && lane == 0) SLLM_TL_HERE(504 + MODE * 10);
     if (!ok) {                       // a wait gave up: give copies in flight time to land before shared memory goes away
         for (int i = 0; i < 64; ++i) __nanosleep(16384);
     }
@@ -332,6 +363,36 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
 }
 
 // ---- small helper kernels of the tensor-core path ------------------------------------------------------
+
+// First layer of a tensor-core pass: gathers the fp32 embedding rows (src/ops/embedding.cpp:20-44) into the residual
+// stream and prepares the first projection's operand in the folded-norm form: bf16(x * gain) and the row's sum of
+// squares in part 0 (the other parts 0).
+__global__ void __launch_bounds__(256) k_embed_prep(const float* __restrict__ emb, const uint32_t* __restrict__ tok_id,
+                                                     const float* __restrict__ gain, float* __restrict__ x_out,
+                                                     __nv_bfloat16* __restrict__ xn, float* __restrict__ ss, int D, int n_parts) {
+    __shared__ float red[8];
+    SLLM_TL(700);
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tok = blockIdx.x;
+    const float* src = emb + (size_t)tok_id[tok] * D;
+    float sum = 0.f;
+    for (int k = threadIdx.x; k < D; k += 256) {
+        const float v = src[k];
+        x_out[(size_t)tok * D + k] = v;
+        xn[(size_t)tok * D + k] = __float2bfloat16_rn(v * gain[k]);
+        sum += v * v;
+    }
+    sum = warp_sum(sum);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < n_parts) {
+        float t = 0.f;
+        if (threadIdx.x == 0)
+            for (int w = 0; w < 8; ++w) t += red[w];
+        ss[(size_t)tok * n_parts + threadIdx.x] = t;
+    }
+}
 // RMSNorm (src/ops/rmsnorm.cpp:38-60) of selected rows to bf16 [n_rows][D]; on layer 0 the row is first
 // gathered from the fp32 embedding table and stored as the residual stream.
 __global__ void __launch_bounds__(256) k_rmsnorm_bf16(const float* __restrict__ x, const float* __restrict__ gain,
