@@ -125,6 +125,7 @@ struct sllm_engine {
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
+    int tune_tc_split = 0;             // SLLM_TC_SPLIT: tuning aid, forces the split-K cluster size of the projections
     int tune_stream_splits = 0;        // SLLM_STREAM_SPLITS: tuning aid, overrides the split count of the streaming kernel
     unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
     float* samp_w = nullptr; float* samp_pmax_val = nullptr; int* samp_pmax_idx = nullptr;
@@ -358,9 +359,37 @@ int x_map(sllm_engine* e, const void* buf, uint64_t rows_cap, uint64_t K, int bn
 }
 
 template <int BN, int MODE>
-int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, bool pdl) {
-    const dim3 grid((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN);
-    return launch(e, k_gemm_tc<BN, MODE>, grid, dim3(kTcThreads), tc_smem_bytes<BN>(), pdl, mw, mx, a);
+int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, bool pdl) {
+    const int tiles = ((a.R + kTcBM - 1) / kTcBM) * ((a.n_tok + BN - 1) / BN);
+    const int nkb = (a.K + kTcBK - 1) / kTcBK;
+    // split-K over a cluster while the tiles alone leave most SMs idle: about 3 K blocks per block at least
+    int split = std::min({kTcMaxSplit, std::max(1, nkb / 3), std::max(1, e->sm_count / tiles)});
+    if (e->tune_tc_split > 0) split = std::min({e->tune_tc_split, kTcMaxSplit, nkb});
+    if (tc_smem_bytes(BN, 2, split) > e->max_dyn_smem) split = 1;
+    const int kb_per_block = (nkb + split - 1) / split;
+    const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split)) / tc_stage_bytes(BN));
+    a.split = split;
+    const int cap = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10));   // beyond this, measured slower (less room for the next kernel's blocks)
+    a.stages = std::max(1, std::min({cap, fit, kb_per_block}));
+    const dim3 grid((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN, split);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = tc_smem_bytes(BN, a.stages, split); cfg.stream = e->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (split > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = split;
+        ++na;
+    }
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr; cfg.numAttrs = na;
+    CU(cudaLaunchKernelEx(&cfg, k_gemm_tc<BN, MODE>, mw, mx, a));
+    e->launches += 1;
+    return SLLM_OK;
 }
 
 // token-tile width: wide tiles for arithmetic intensity, narrower ones while the grid would not fill the GPU
@@ -395,10 +424,10 @@ int configure_tc(sllm_engine* e) {
         if (!rc && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
             rc = fail(e, SLLM_ERR_CUDA, "cudaFuncSetAttribute failed for the tensor-core projection kernel");
     };
-    set(k_gemm_tc<32, MODE>, tc_smem_bytes<32>());
-    set(k_gemm_tc<64, MODE>, tc_smem_bytes<64>());
-    set(k_gemm_tc<128, MODE>, tc_smem_bytes<128>());
-    set(k_gemm_tc<256, MODE>, tc_smem_bytes<256>());
+    set(k_gemm_tc<32, MODE>, e->max_dyn_smem);
+    set(k_gemm_tc<64, MODE>, e->max_dyn_smem);
+    set(k_gemm_tc<128, MODE>, e->max_dyn_smem);
+    set(k_gemm_tc<256, MODE>, e->max_dyn_smem);
     return rc;
 }
 
@@ -1062,6 +1091,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     e->n_pages = (opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq) + 1;   // + the spare page
     e->spare_page = (int)(e->n_pages - 1);
     if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
+    if (const char* v = std::getenv("SLLM_TC_SPLIT")) e->tune_tc_split = std::max(0, std::atoi(v));
     if (const char* v = std::getenv("SLLM_STREAM_SPLITS")) e->tune_stream_splits = std::min(std::max(0, std::atoi(v)), 8);
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);

@@ -22,6 +22,8 @@ namespace sllm {
 constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
 constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int kTcThreads = 320;
+constexpr int kTcMaxStages = 16;
+constexpr int kTcMaxSplit = 8;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // a wait gives up after two seconds
 
 struct TcArgs {
@@ -44,6 +46,12 @@ struct TcArgs {
     const float* ss_in;             // QKV / GateUp: the same array, written by the producer (null: operand already normalised)
     int n_parts;
     float eps;
+    // Split-K over a thread-block cluster (grid z = cluster z = split): block z accumulates its share of the K
+    // blocks in its own tensor memory; blocks 1.. hand their accumulators to block 0 through distributed shared
+    // memory, block 0 adds them in rank order and runs the epilogue.  With few tiles (small batches) this spreads a
+    // tile's weight bytes over several SMs, each of which can only take in ~65 GB/s.
+    int stages;                     // pipeline stages of this launch (<= kTcMaxStages)
+    int split;                      // blocks per cluster (1 = no cluster)
 };
 
 // Sums v[j] over the 32 lanes for every j at once: afterwards lane j holds the sum of all lanes' v[j] (31 shuffles,
@@ -136,29 +144,51 @@ template <int CW> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t
     if (CW == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
 }
 
-// as many stages as shared memory holds: a block's throughput is its bytes in flight over the copy latency
-template <int BN> __host__ __device__ constexpr int tc_stages() { return BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10)); }
-template <int BN> __host__ __device__ constexpr size_t tc_smem_bytes() {
-    return 1024 + (size_t)tc_stages<BN>() * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + 256 + 4 * 2 * BN * sizeof(int);
+// Shared memory of one block: [1 KB alignment slack][stages x (weight tile | token tile)][barriers, TMEM slot: 512 B]
+// [token metadata: 8 warps x (BN ints + BN/2 floats)][split > 1: (split - 1) accumulators of 128 x BN floats handed over
+// by the peers]
+constexpr size_t tc_stage_bytes(int bn) { return (size_t)kTcBM * kTcBK * 2 + (size_t)bn * kTcBK * 2; }
+constexpr size_t tc_fixed_bytes(int bn, int split) {
+    return 1024 + 512 + (size_t)12 * bn * sizeof(int) + (size_t)(split - 1) * kTcBM * bn * sizeof(float);
+}
+constexpr size_t tc_smem_bytes(int bn, int stages, int split) { return tc_fixed_bytes(bn, split) + (size_t)stages * tc_stage_bytes(bn); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in the cluster's block `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ CUtensorMap map_w,
                                                         const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
-    constexpr int STAGES = tc_stages<BN>();
     constexpr uint32_t A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2;
+    const int STAGES = a.stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[S], empty[S], done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
-    int* tok_meta = reinterpret_cast<int*>(tmem_slot + 2);                  // [8 epilogue warps][pos[BN/2] | page[BN/2]]
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[16], empty[16], done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcMaxStages + 1);
+    int* tok_meta = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);   // [8 epilogue warps][pos[BN/2] | page[BN/2]]
+    float* tok_rs = reinterpret_cast<float*>(tok_meta + 8 * BN);            // [8 epilogue warps][BN/2]: 1/rms of the warp's tokens
+    float* handover = tok_rs + 4 * BN;                                      // [split - 1][BN][128] in block 0 of the cluster
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcMaxStages), done_bar = smem_u32(bars + 2 * kTcMaxStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kTcBM, t0 = blockIdx.y * BN;
-    const int nkb = (a.K + kTcBK - 1) / kTcBK;
+    const int split = a.split, ks = blockIdx.z;                             // the cluster spans grid z
+    const int nkb_all = (a.K + kTcBK - 1) / kTcBK;
+    const int kb_first = (nkb_all * ks) / split;
+    const int nkb = (nkb_all * (ks + 1)) / split - kb_first;                // this block's K blocks (>= 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -182,7 +212,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     if (warp == 0 && lane == 0) {
         for (int kb = 0; kb < pre; ++kb) {
             mbar_expect_tx(full0 + 8 * kb, A_BYTES + B_BYTES);
-            tma_load_2d(smem_u32(sA + kb * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * kb);
+            tma_load_2d(smem_u32(sA + kb * A_BYTES), &map_w, (kb_first + kb) * kTcBK, m0, full0 + 8 * kb);
         }
     }
     pdl_wait();
@@ -191,23 +221,28 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
+            // stage index and round kept as counters: the stage count is a launch parameter, and an integer
+            // division per K block on this single thread would be on the critical path
+            int s = 0; uint32_t round = 0;
             for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % STAGES;
                 if (kb >= pre) {
-                    ok = mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, a.status, 11);
+                    ok = mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.status, 11);
                     if (!ok) break;
                     mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
-                    tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, kb * kTcBK, m0, full0 + 8 * s);
+                    tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, (kb_first + kb) * kTcBK, m0, full0 + 8 * s);
                 }
-                tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, kb * kTcBK, t0, full0 + 8 * s);
+                tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, (kb_first + kb) * kTcBK, t0, full0 + 8 * s);
+                if (++s == STAGES) { s = 0; ++round; }
             }
         }
+        __syncwarp();
+        if (split > 1) cluster_sync_all();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = tc_idesc(kTcBM, BN);
+            int s = 0; uint32_t round = 0;
             for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, a.status, 12);
+                ok = mbar_wait(full0 + 8 * s, round & 1, a.status, 12);
                 if (!ok) break;
                 tc_fence_after();
                 if (kb == 0) SLLM_TL_HERE(502 + MODE * 10);
@@ -217,9 +252,12 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 for (int k = 0; k < kTcBK / 16; ++k)
                     tc_mma_bf16(tmem, tc_smem_desc(aaddr + k * 32), tc_smem_desc(baddr + k * 32), idesc, (kb | k) != 0);
                 tc_commit(empty0 + 8 * s);          // the stage may be refilled once these MMAs have read it
+                if (++s == STAGES) { s = 0; ++round; }
             }
             if (ok) tc_commit(done_bar);            // accumulator complete
         }
+        __syncwarp();
+        if (split > 1) cluster_sync_all();
     } else {
         // ---- epilogue: warps 2..9; warp w reads TMEM lane quarter w % 4, columns of half (w - 2) / 4 -------
         constexpr int HALF = BN / 2;                             // token columns per epilogue warp
@@ -251,17 +289,32 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         }
         float2 cs[MODE == kModeQKV ? CW : 1];
         float xv[MODE == kModeResidual ? CW : 1];
-        float rs = 1.0f;                                         // lane j: 1/rms of token column c + j (consumers of a folded norm)
         const bool scaled = (MODE == kModeQKV || MODE == kModeGateUp) && a.ss_in != nullptr;
         const float gnext = (MODE == kModeResidual && a.gain_next && row_ok) ? a.gain_next[row] : 0.f;
-        auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
-            if (scaled) {
-                const int tok = t0 + c + lane;
-                float ss = 0.f;
-                if (lane < CW && tok < a.n_tok)
-                    for (int p = 0; p < a.n_parts; ++p) ss += a.ss_in[(size_t)tok * a.n_parts + p];
-                rs = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+        // consumers of a folded norm: 1/rms of each of the warp's tokens, from the producer's partial sums of squares
+        float* my_rs = tok_rs + ew * HALF;
+        if (MODE == kModeQKV || MODE == kModeGateUp) {
+            for (int j = lane; j < HALF; j += 32) {
+                const int tok = t0 + cbeg + j;
+                float r = 1.0f;
+                if (scaled && ks == 0 && tok < a.n_tok) {        // n_parts is a multiple of 4: 16-byte loads, 8 in flight per trip
+                    const float4* pp = reinterpret_cast<const float4*>(a.ss_in + (size_t)tok * a.n_parts);
+                    const int n4 = a.n_parts / 4;
+                    float ss = 0.f;
+                    for (int p0 = 0; p0 < n4; p0 += 8) {
+                        float4 q[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) q[i] = p0 + i < n4 ? pp[p0 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) ss += (q[i].x + q[i].y) + (q[i].z + q[i].w);
+                    }
+                    r = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+                }
+                my_rs[j] = r;
             }
+            __syncwarp();
+        }
+        auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
             if (MODE == kModeQKV) {
 #pragma unroll
                 for (int j = 0; j < CW; ++j)
@@ -274,16 +327,35 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 }
             }
         };
-        if (t0 + cbeg < a.n_tok) fetch(cbeg);
+        if (ks == 0 && t0 + cbeg < a.n_tok) fetch(cbeg);
         ok = mbar_wait(done_bar, 0, a.status, 13);
         ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
         tc_fence_after();
         if (warp == 2 && lane == 0) SLLM_TL_HERE(503 + MODE * 10);
-        for (int c0 = cbeg; c0 < cbeg + HALF && ok; c0 += CW) {
+        if (split > 1) {
+            if (ks > 0 && ok) {                                  // hand this block's accumulator to block 0: [peer][column][row]
+                const uint32_t base = cluster_map(smem_u32(handover), 0);
+                for (int c0 = cbeg; c0 < cbeg + HALF; c0 += CW) {
+                    if (t0 + c0 >= a.n_tok) break;
+                    uint32_t v[CW];
+                    tc_ld<CW>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < CW; ++j)
+                        st_cluster_f32(base + 4u * (uint32_t)(((ks - 1) * BN + c0 + j) * kTcBM + quarter * 32 + lane), __uint_as_float(v[j]));
+                }
+            }
+            cluster_sync_all();                                  // every thread of every block of the cluster, exactly once
+        }
+        for (int c0 = cbeg; c0 < cbeg + HALF && ok && ks == 0; c0 += CW) {
             if (t0 + c0 >= a.n_tok) break;                       // uniform over the warp
             const bool more = c0 + CW < cbeg + HALF && t0 + c0 + CW < a.n_tok;
             uint32_t v[CW];
             tc_ld<CW>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+            for (int p = 0; p + 1 < split; ++p) {                // peers' shares, in rank order
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                    v[j] = __float_as_uint(__uint_as_float(v[j]) + handover[((p * BN + c0 + j) * kTcBM) + quarter * 32 + lane]);
+            }
             if (MODE == kModeResidual) {
                 float r[CW];
 #pragma unroll
@@ -317,19 +389,18 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 const bool store_lane = row_ok && (row & 1) == 0;
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs, j);
+                    const float acc = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
                     const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
                     const float hval = __fdividef(acc, 1.0f + __expf(-acc)) * other;
                     const int tok = t0 + c0 + j;
                     if (store_lane && tok < a.n_tok) a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn(hval);
                 }
-                if (more) fetch(c0 + CW);
             } else {
                 // RoPE pairs sit in adjacent lanes
                 float r[CW];
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs, j);
+                    const float acc = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
                     const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
                     r[j] = acc;
                     if (which < 2) r[j] = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
