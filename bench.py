@@ -232,7 +232,7 @@ def run_ours(args):
             line["profile_only"] = True
         if args.cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -306,7 +306,7 @@ def run_c4(args):
     if rank == 0:
         peak, kind = peaks()
         achieved = float(by[0]) / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        emit(({
             "metric": "decode tok/s at batch 512 vs HBM roofline", "value": float(tok_local[0]) / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms / args.steps,
             "per_iteration_ms": ms / n_iter, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -382,7 +382,7 @@ def run_reference(args):
     value = 1.0 / dt
     sample = (f"each step = one token of the reference's own loop on CPU (full forward over a {window}-id window, no KV "
               f"cache, + host sampler); configured window {N_PROMPT}..{N_PROMPT + N_NEW - 1}, cost linear in the window")
-    print(json.dumps({
+    emit(({
         "impl": "reference", "metric": METRIC,
         "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -393,8 +393,25 @@ def run_reference(args):
     }))
 
 
+_REAL_STDOUT = None
+
+
+def emit(line: dict):
+    """The one JSON line, on the process's real standard output."""
+    text = json.dumps(line) + "\n"
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text); sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, text.encode())
+
+
 def main():
-    global N_NEW
+    global N_NEW, _REAL_STDOUT
+    # Libraries print to standard output on their own (the collective library announces its version there when the
+    # process group comes up): everything but the JSON line goes to standard error instead.
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)

@@ -325,3 +325,30 @@ def test_eval_loss_matches_reference_cross_entropy(fp32, golden_dir):
     assert abs(eng.eval_loss(ids, targets, 3, 40, n) - ref) <= tol
     with pytest.raises(ValueError, match="outside the vocabulary"):
         eng.eval_loss(ids, np.full(120, SMALL.vocab, np.int32), 3, 40)
+
+
+@pytest.mark.parametrize("split", [2, 4])
+def test_split_k_cluster_projections(split, monkeypatch):
+    """The tensor-core projections with their K blocks dealt over a thread-block cluster (forced here; the engine
+    chooses it by itself only when few tiles exist): same logits as the oracle within the bf16 tolerance, and the
+    same as the unsplit kernel up to the rounding of intermediate activations."""
+    cfg = MID                                               # K = 128 (2 K blocks) and 200 (4, the last one ragged)
+    ids = prompt_ids(1, 2 * 100, cfg.vocab)
+    monkeypatch.setenv("SLLM_TC_SPLIT", "1")
+    o, eng1 = make_pair(cfg, seed=3, stddev=0.05, fp32=False, max_batch=2, via_checkpoint=False)
+    base = eng1.forward_logits(ids, 2, 100)
+    monkeypatch.setenv("SLLM_TC_SPLIT", str(split))
+    _, eng = make_pair(cfg, seed=3, stddev=0.05, fp32=False, max_batch=2, via_checkpoint=False)
+    got = eng.forward_logits(ids, 2, 100)
+    ref = o.forward(ids, 2, 100)
+    assert rel_err(got, ref) <= TOL_BF16
+    assert rel_err(got, base) <= 5e-3
+    # decode at 20 sequences goes through the same kernels with one token per sequence
+    prompts = [prompt_ids(10 + i, 30 + i, cfg.vocab) for i in range(20)]
+    _, engb = make_pair(cfg, seed=3, stddev=0.05, fp32=False, max_batch=20, via_checkpoint=False)
+    engb.prefill(prompts)
+    engb.decode_loop(3, SamplingOptions(temperature=0.0, repetition_penalty=1.0), None, eos=cfg.vocab + 5)
+    for i in (0, 7, 19):
+        toks = engb.tokens(i)
+        assert toks.size == prompts[i].size + 3
+        assert rel_err(engb.step_logits(i), o.forward(toks, 1, toks.size)[0, -1]) <= TOL_BF16
