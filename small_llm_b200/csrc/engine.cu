@@ -24,6 +24,7 @@
 #include "../../include/sllm.h"
 #include "attn_decode.cuh"
 #include "attn_prefill.cuh"
+#include "attn_prefill_tc.cuh"
 #include "attn_stream.cuh"
 #include "common.cuh"
 #include "decode_fused.cuh"
@@ -114,6 +115,9 @@ struct sllm_engine {
     void* encode_tiled = nullptr;                    // cuTensorMapEncodeTiled
     std::vector<CUtensorMap> map_wqkv, map_wo, map_wgu, map_wd;
     CUtensorMap map_head{};
+    CUtensorMap map_kv{};                            // the KV pool as [rows][64] bf16 (head_dim 64): K pages by TMA
+    bool attn_tc = false;                            // tensor-core prefill attention usable (bf16, head_dim 64)
+    int pf_tile_q = kPfQ;                            // queries per prefill tile (128 with the tensor-core kernel)
     std::map<std::pair<const void*, int>, CUtensorMap> map_x;    // (activation buffer, BN) -> map
     int tc_min_tokens = 17;
     // fused single-token decode path
@@ -249,6 +253,12 @@ int launch_attn_prefill_hd(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
 template <typename KVT>
 int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
     if (a.pass.n_tiles > 0 && a.pass.n_tiles * 4 <= a.pass.n_tok) {      // long runs of one sequence: query tiles share the pages
+        if (e->attn_tc && sizeof(KVT) == 2) {
+            AttnPtArgs p{};
+            p.q = a.q; p.out = a.out; p.out_bf16 = a.out_bf16; p.m = a.m; p.kv = a.kv; p.tiles = a.pass.tiles; p.layer = a.layer;
+            p.status = e->d_status;
+            return launch(e, k_attn_prefill_tc, dim3(a.pass.n_tiles, a.m.H), dim3(kPtThreads), attn_prefill_tc_smem(), pdl, e->map_kv, p);
+        }
         switch (a.m.hd) {
             case 16: return launch_attn_prefill_hd<KVT, 16>(e, a, pdl);
             case 32: return launch_attn_prefill_hd<KVT, 32>(e, a, pdl);
@@ -1010,7 +1020,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
             const int slot = slot_ids ? slot_ids[s] : (int)s;
             const int pos = (pos0s ? pos0s[s] : 0) + (int)i;
             if (host_logits || h_targets || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
-            if (!c_tiles.empty() && c_tiles.back().slot == slot && c_tiles.back().n_q < kPfQ &&
+            if (!c_tiles.empty() && c_tiles.back().slot == slot && c_tiles.back().n_q < e->pf_tile_q &&
                 c_tiles.back().pos0 + c_tiles.back().n_q == pos && c_tiles.back().tok_begin + c_tiles.back().n_q == (int)c_id.size())
                 c_tiles.back().n_q += 1;
             else
@@ -1231,6 +1241,16 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             if (!rc) rc = make_map(e, &e->map_wd[l], e->layers[l].wd, D, F, kTcBM);
         }
         if (!rc) rc = make_map(e, &e->map_head, e->emb_w, V, D, kTcBM);
+        // tensor-core prefill attention: head_dim 64, the pool as one [rows][64] tensor whose rows fit a TMA coordinate
+        const unsigned long long kv_rows = (unsigned long long)L * (unsigned long long)e->n_pages * 2ull * H * kPage;
+        if (!rc && hd == 64 && kv_rows < (1ull << 31) && std::getenv("SLLM_NO_ATTN_TC") == nullptr) {
+            rc = make_map(e, &e->map_kv, e->kv_pool, kv_rows, 64, kPage);
+            if (!rc && cudaFuncSetAttribute(k_attn_prefill_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)attn_prefill_tc_smem()) != cudaSuccess) {
+                e->err = "cudaFuncSetAttribute failed for the prefill attention kernel"; rc = SLLM_ERR_CUDA;
+            }
+            if (!rc) { e->attn_tc = true; e->pf_tile_q = kPtQ; }
+        }
         if (!rc) rc = configure_tc<kModeQKV>(e);
         if (!rc) rc = configure_tc<kModeResidual>(e);
         if (!rc) rc = configure_tc<kModeGateUp>(e);
