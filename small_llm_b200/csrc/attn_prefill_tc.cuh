@@ -10,16 +10,18 @@
 // Operands in shared memory are K-major with the 128-byte swizzle: K pages come in by TMA over the whole KV pool
 // (a [rows][64] bf16 tensor), V pages by a bulk copy and are transposed to [dim][key] by four warps, Q (fp32 from
 // the projection) and P are written by the threads themselves in the swizzled layout.
-// Warps: 0 = copy producer, 1 = MMA issuer and TMEM owner, 2-5 = softmax (TMEM lane quarters 2,3,0,1),
-// 6-9 = V transposers.  S is double-buffered in TMEM so that S of the next page is computed while the softmax of this
-// one runs.  Every mbarrier wait is bounded (two seconds), as in gemm_tc.cuh.
+// Warps: 0 = copy producer, 1 = MMA issuer and TMEM owner, 2-5 = softmax (TMEM lane quarters 2,3,0,1); the softmax
+// warps also transpose the next page's V while the PV product of this page runs.  S is double-buffered in TMEM so that
+// S of the next page is computed while the softmax of this one runs.  192 threads at <= 168 registers and 97 KB of
+// shared memory: two blocks per SM, which overlap each other's dependency chains.  Every mbarrier wait is bounded
+// (two seconds), as in gemm_tc.cuh.
 #pragma once
 #include "attn_stream.cuh"
 #include "gemm_tc.cuh"
 
 namespace sllm {
 
-constexpr int kPtThreads = 320;
+constexpr int kPtThreads = 192;
 constexpr int kPtQ = 128;                    // query rows per tile (UMMA M)
 constexpr int kPtStages = 3;                 // K / raw-V pages in flight
 constexpr uint32_t kPtPageBytes = kPage * 64 * 2;           // one page of K (or V) of one head: 8 KB
@@ -54,7 +56,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_constant__ CUtensorMap map_kv, const AttnPtArgs a) {
+__global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_constant__ CUtensorMap map_kv, const AttnPtArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
@@ -64,8 +66,8 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
     uint8_t* sP = sVt + 2 * kPtPageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPtQ * 128);
     // barrier indices
-    enum { K_FULL = 0, V_FULL = 3, K_FREE = 6, V_FREE = 9, S_READY = 12, S_FREE = 14, VT_READY = 16, VT_FREE = 18,
-           P_READY = 20, PV_READY = 21, N_BARS = 22 };
+    enum { K_FULL = 0, V_FULL = 3, K_FREE = 6, V_FREE = 9, S_READY = 12, S_FREE = 14, VT_READY = 16, P_READY = 18,
+           PV_READY = 19, N_BARS = 20 };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     const uint32_t bar0 = smem_u32(bars);
     auto B = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 3; ++i) { mbar_init(B(K_FULL + i), 1); mbar_init(B(V_FULL + i), 1); mbar_init(B(K_FREE + i), 1); mbar_init(B(V_FREE + i), 4); }
-        for (int i = 0; i < 2; ++i) { mbar_init(B(S_READY + i), 1); mbar_init(B(S_FREE + i), 4); mbar_init(B(VT_READY + i), 4); mbar_init(B(VT_FREE + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(B(S_READY + i), 1); mbar_init(B(S_FREE + i), 4); mbar_init(B(VT_READY + i), 4); }
         mbar_init(B(P_READY), 4); mbar_init(B(PV_READY), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -157,11 +159,10 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
                 for (int k = 0; k < 4; ++k)
                     tc_mma_bf16(tmem + 128u, tc_smem_desc(pa + k * 32), tc_smem_desc(vb + k * 32), idesc, k != 0);
                 tc_commit(B(PV_READY));
-                tc_commit(B(VT_FREE + b));
             }
         }
-    } else if (warp < 6) {
-        // ---- softmax: thread = query row = TMEM lane ----------------------------------------------------
+    } else {
+        // ---- softmax: thread = query row = TMEM lane; transposition of V: thread = (dim, half of the keys) ----
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const int qpos = t.pos0 + r;
@@ -170,7 +171,33 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
 #pragma unroll
         for (int d = 0; d < 64; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
-        for (int i = 0; i < n_pages; ++i) {
+        const int tt = threadIdx.x - 64, h = tt & 63, half = tt >> 6;
+        // page [key][dim] -> [dim][key], K-major swizzled, into buffer i & 1.  The buffer was last read by the PV
+        // product of page i - 2, whose completion this thread has already waited for.
+        auto transpose_v = [&](int i) -> bool {
+            const int s = i % kPtStages;
+            bool good = mbar_wait(B(V_FULL + s), (i / kPtStages) & 1, a.status, 39);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
+            const unsigned short* src = reinterpret_cast<const unsigned short*>(sVraw + s * kPtPageBytes) + (half * 32) * 64 + h;
+            uint8_t* dst = sVt + (i & 1) * kPtPageBytes;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t lo = src[(c * 8 + 2 * e) * 64], hi = src[(c * 8 + 2 * e + 1) * 64];
+                    w[e] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint4*>(dst + sw128(h, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(B(VT_READY + (i & 1))); mbar_arrive(B(V_FREE + s)); }
+            return true;
+        };
+        ok = transpose_v(0);
+        for (int i = 0; i < n_pages && ok; ++i) {
             const int b = i & 1;
             ok = mbar_wait(B(S_READY + b), (i >> 1) & 1, a.status, 37);
             ok = __all_sync(0xffffffffu, ok);
@@ -209,6 +236,7 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
             tc_fence_before();                                   // the PV loads of the previous page are done before the next PV may start
             __syncwarp();
             if (lane == 0) mbar_arrive(B(P_READY));
+            if (i + 1 < n_pages && !transpose_v(i + 1)) { ok = false; break; }   // while the PV product of this page runs
             ok = mbar_wait(B(PV_READY), i & 1, a.status, 38);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -231,32 +259,6 @@ __global__ void __launch_bounds__(kPtThreads) k_attn_prefill_tc(const __grid_con
                     d16[c] = make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
                                         pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
             }
-        }
-    } else {
-        // ---- V transposers: page [key][dim] -> [dim][key], K-major swizzled ------------------------------
-        const int tt = threadIdx.x - 192;              // 0..127
-        const int h = tt & 63, half = tt >> 6;         // this thread: dim h, keys half*32 .. +31
-        for (int i = 0; i < n_pages; ++i) {
-            const int s = i % kPtStages, b = i & 1;
-            ok = mbar_wait(B(V_FULL + s), (i / kPtStages) & 1, a.status, 39);
-            if (ok && i >= 2) ok = mbar_wait(B(VT_FREE + b), ((i >> 1) - 1) & 1, a.status, 40);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const unsigned short* src = reinterpret_cast<const unsigned short*>(sVraw + s * kPtPageBytes) + (half * 32) * 64 + h;
-            uint8_t* dst = sVt + b * kPtPageBytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t lo = src[(c * 8 + 2 * e) * 64], hi = src[(c * 8 + 2 * e + 1) * 64];
-                    w[e] = lo | (hi << 16);
-                }
-                *reinterpret_cast<uint4*>(dst + sw128(h, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(B(VT_READY + b)); mbar_arrive(B(V_FREE + s)); }
         }
     }
     if (!ok) {                       // a wait gave up: give copies in flight time to land before shared memory goes away
