@@ -383,7 +383,7 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, T
     a.stages = std::max(1, std::min({cap, fit, kb_per_block}));
     const dim3 grid((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN, split);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid; cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = tc_smem_bytes(BN, a.stages, split); cfg.stream = e->stream;
+    cfg.gridDim = grid; cfg.blockDim = dim3(tc_threads<BN>()); cfg.dynamicSmemBytes = tc_smem_bytes(BN, a.stages, split); cfg.stream = e->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
     if (split > 1) {

@@ -6,8 +6,8 @@
 //
 // The weight tile is the MMA's M side (128 rows = 128 TMEM lanes), the token tile its N side
 // (32..256 columns), so the batch does not have to fill a 128-row tile.  One thread block computes
-// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..9 =
-// epilogue (each reads 32 TMEM lanes of one half of the columns; thread = weight row, registers = tokens).  The same fused
+// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2.. (8 or 16 of them) =
+// epilogue (each reads 32 TMEM lanes of one half or quarter of the columns; thread = weight row, registers = tokens).  The same fused
 // epilogues as the GEMV family: RoPE + paged-KV append, residual add, SiLU(gate)*up, fp32 logits.
 // Every mbarrier wait is bounded; on expiry the block raises the engine's status word, lets its
 // copies land, frees its tensor memory and returns.
@@ -21,7 +21,11 @@ namespace sllm {
 
 constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
 constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
-constexpr int kTcThreads = 320;
+// Epilogue warps: 8 (two per TMEM lane quarter) for narrow token tiles, 16 for wide ones, where the epilogue (loads
+// from L2 and stores scattered by token, a few per warp in flight) takes longer than the main loop: more warps keep
+// more of them in flight.
+template <int BN> __host__ __device__ constexpr int tc_epi_warps() { return BN >= 128 ? 16 : 8; }
+template <int BN> __host__ __device__ constexpr int tc_threads() { return 64 + 32 * tc_epi_warps<BN>(); }
 constexpr int kTcMaxStages = 16;
 constexpr int kTcMaxSplit = 8;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // a wait gives up after two seconds
@@ -145,7 +149,7 @@ template <int CW> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t
 }
 
 // Shared memory of one block: [1 KB alignment slack][stages x (weight tile | token tile)][barriers, TMEM slot: 512 B]
-// [token metadata: 8 warps x (BN ints + BN/2 floats)][split > 1: (split - 1) accumulators of 128 x BN floats handed over
+// [token metadata: per epilogue warp its columns' positions, pages and 1/rms: 12 x BN words in all][split > 1: (split - 1) accumulators of 128 x BN floats handed over
 // by the peers]
 constexpr size_t tc_stage_bytes(int bn) { return (size_t)kTcBM * kTcBK * 2 + (size_t)bn * kTcBK * 2; }
 constexpr size_t tc_fixed_bytes(int bn, int split) {
@@ -168,7 +172,7 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_constant__ CUtensorMap map_w,
                                                         const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
     constexpr uint32_t A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2;
     const int STAGES = a.stages;
@@ -178,8 +182,8 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     uint8_t* sB = smem + STAGES * A_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[16], empty[16], done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcMaxStages + 1);
-    int* tok_meta = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);   // [8 epilogue warps][pos[BN/2] | page[BN/2]]
-    float* tok_rs = reinterpret_cast<float*>(tok_meta + 8 * BN);            // [8 epilogue warps][BN/2]: 1/rms of the warp's tokens
+    int* tok_meta = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);   // [epilogue warps][pos | page of the warp's columns]
+    float* tok_rs = reinterpret_cast<float*>(tok_meta + 8 * BN);            // [epilogue warps][its columns]: 1/rms of the warp's tokens
     float* handover = tok_rs + 4 * BN;                                      // [split - 1][BN][128] in block 0 of the cluster
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcMaxStages), done_bar = smem_u32(bars + 2 * kTcMaxStages);
 
@@ -259,9 +263,10 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         __syncwarp();
         if (split > 1) cluster_sync_all();
     } else {
-        // ---- epilogue: warps 2..9; warp w reads TMEM lane quarter w % 4, columns of half (w - 2) / 4 -------
-        constexpr int HALF = BN / 2;                             // token columns per epilogue warp
-        constexpr int CW = HALF >= 32 ? 32 : 16;                 // columns per TMEM load
+        // ---- epilogue: warp w reads TMEM lane quarter w % 4, column group (w - 2) / 4 -------------------------
+        constexpr int EW = tc_epi_warps<BN>();
+        constexpr int HALF = BN / (EW / 4);                      // token columns per epilogue warp
+        constexpr int CW = (EW == 16 || HALF < 32) ? 16 : 32;    // columns per TMEM load
         const int ew = warp - 2;
         const int quarter = warp & 3;
         const int cbeg = (ew >> 2) * HALF;
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         // While the tensor cores work, each epilogue warp fetches the positions and KV pages of its tokens into
         // its own shared-memory copy, and the operands of its first column chunk that do not depend on the
         // accumulator (rotation factors, residual values), so that little is left to wait for afterwards.
-        int* my_pos = tok_meta + ew * BN;
+        int* my_pos = tok_meta + ew * 2 * HALF;
         int* my_page = my_pos + HALF;
         if (MODE == kModeQKV) {
             for (int j = lane; j < HALF; j += 32) {
