@@ -27,6 +27,7 @@ struct AttnDecArgs {
     float* part_o;         // [n_tok][H][n_splits][hd]
     float* part_ml;        // [n_tok][H][n_splits][2]
     unsigned int* ticket;  // [n_tok][H], zero between launches
+    int prefer_stream;     // host side: take the page-streaming kernel although there are fewer pairs than SMs
 };
 
 constexpr int kAttnThreads = 128;

@@ -119,7 +119,7 @@ struct sllm_engine {
     bool attn_tc = false;                            // tensor-core prefill attention usable (bf16, head_dim 64)
     int pf_tile_q = kPfQ;                            // queries per prefill tile (128 with the tensor-core kernel)
     std::map<std::pair<const void*, int>, CUtensorMap> map_x;    // (activation buffer, BN) -> map
-    int tc_min_tokens = 17;
+    int tc_min_tokens = 2;                           // measured: from 2 tokens on the tensor-core pass beats the GEMV family (0.48 vs 0.51 ms at 2 sequences, 0.53 vs 1.40 ms at 8)
     // fused single-token decode path
     float* xb = nullptr; float* attn_parts = nullptr; float* down_parts = nullptr;
     std::vector<void*> wdT;                          // per layer: down weights as [F][D]
@@ -266,7 +266,7 @@ int launch_attn(sllm_engine* e, const AttnDecArgs& a, bool pdl) {
             case 128: return launch_attn_prefill_hd<KVT, 128>(e, a, pdl);
         }
     }
-    if ((a.n_splits == 1 || a.pass.n_tok * a.m.H >= e->sm_count) && e->use_attn_stream) {   // stream pages through shared memory
+    if ((a.prefer_stream || a.n_splits == 1 || a.pass.n_tok * a.m.H >= e->sm_count) && e->use_attn_stream) {   // stream pages through shared memory
         switch (a.m.hd) {
             case 16: return launch_attn_stream_hd<KVT, 16>(e, a, pdl);
             case 32: return launch_attn_stream_hd<KVT, 32>(e, a, pdl);
@@ -468,17 +468,19 @@ int run_pass_tc(sllm_engine* e, const PassView& pv, const int* row_tok, int n_ro
         if (rc) return rc;
         AttnDecArgs t{};
         t.q = e->q; t.out = e->att; t.out_bf16 = e->att16; t.m = m; t.kv = kv; t.pass = pv; t.layer = l;
-        // few (token, head) pairs: split each one's pages over up to 4 blocks, about 8 blocks per SM in all
-        // (measured at 32 and 64 sequences: 4 splits and 1 split are the fastest); none once the pairs alone
-        // fill the 4 resident blocks per SM
         {
             const int pairs = n * m.H;
             t.n_splits = 1;
-            if (pv.n_tiles == 0 && n <= e->split_tok_cap && pairs < 4 * e->sm_count)
-                t.n_splits = std::max(1, std::min(4, (8 * e->sm_count + pairs / 2) / pairs));
+            t.keys_per_split = e->pages_per_seq * kPage;
+            if (pv.n_tiles == 0 && n <= e->split_tok_cap && pairs < 4 * e->sm_count) {
+                // the streaming kernel: split each pair's pages over several blocks, about 8 blocks per SM in all
+                // (measured at 32 and 64 sequences: 4 splits and 1 split are the fastest; at 8 sequences 8 splits);
+                // none once the pairs alone fill the 4 resident blocks per SM
+                t.n_splits = std::max(1, std::min(pairs < e->sm_count ? 8 : 4, (8 * e->sm_count + pairs / 2) / pairs));
+                t.prefer_stream = 1;
+            }
         }
         if (e->tune_stream_splits > 0 && pv.n_tiles == 0 && n <= e->split_tok_cap) t.n_splits = e->tune_stream_splits;
-        t.keys_per_split = e->pages_per_seq * kPage;
         t.part_o = e->part_o; t.part_ml = e->part_ml; t.ticket = e->ticket;
         rc = launch_attn_any(e, t, pdl);
         if (rc) return rc;

@@ -1,4 +1,4 @@
-// Dense projections for many tokens (prefill, decode at batch >= 17) on the 5th-generation tensor
+// Dense projections for two and more tokens (prefill, batched decode) on the 5th-generation tensor
 // cores: tcgen05.mma with the accumulator in tensor memory, operands staged in shared memory by
 // TMA (cp.async.bulk.tensor, no multicast), bf16 x bf16 -> fp32.
 //

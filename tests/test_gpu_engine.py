@@ -352,3 +352,21 @@ def test_split_k_cluster_projections(split, monkeypatch):
         toks = engb.tokens(i)
         assert toks.size == prompts[i].size + 3
         assert rel_err(engb.step_logits(i), o.forward(toks, 1, toks.size)[0, -1]) <= TOL_BF16
+
+
+def test_gemv_family_for_small_bf16_passes(monkeypatch):
+    """bf16 passes of 2 and more tokens take the tensor-core kernels by default; the weight-streaming GEMV family
+    (what runs when the driver offers no tensor-map encoder, and in fp32 mode) is forced here: prefill of ragged
+    prompts and decode steps against the oracle."""
+    monkeypatch.setenv("SLLM_TC_MIN_TOKENS", "100000")
+    cfg = MID
+    o, eng = make_pair(cfg, seed=7, stddev=0.05, fp32=False, max_batch=5, via_checkpoint=False)
+    prompts = [prompt_ids(30 + i, n, cfg.vocab) for i, n in enumerate([3, 70, 1, 129, 40])]
+    eng.prefill(prompts)
+    for i, p in enumerate(prompts):
+        assert rel_err(eng.step_logits(i), o.forward(p, 1, p.size)[0, -1]) <= TOL_BF16
+    eng.decode_loop(4, SamplingOptions(temperature=0.0, repetition_penalty=1.0), None, eos=cfg.vocab + 5)
+    for i, p in enumerate(prompts):
+        toks = eng.tokens(i)
+        assert toks.size == p.size + 4
+        assert rel_err(eng.step_logits(i), o.forward(toks, 1, toks.size)[0, -1]) <= TOL_BF16
