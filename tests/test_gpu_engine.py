@@ -370,3 +370,19 @@ def test_gemv_family_for_small_bf16_passes(monkeypatch):
         toks = eng.tokens(i)
         assert toks.size == p.size + 4
         assert rel_err(eng.step_logits(i), o.forward(toks, 1, toks.size)[0, -1]) <= TOL_BF16
+
+
+def test_sampler_with_one_block_per_slot_at_large_batch():
+    """At 300 and more slots the sampler's partial kernels get a single block per slot (each thread then walks
+    many vocabulary entries) and the attention grid is ordered longest sequence first: sampled streams of a few
+    slots against the oracle."""
+    cfg = SMALL
+    n_seq, n_new = 320, 12
+    o, eng = make_pair(cfg, seed=3, stddev=0.2, fp32=True, max_batch=n_seq, via_checkpoint=False)
+    prompts = [prompt_ids(200 + i, 3 + (i * 7) % 40, cfg.vocab) for i in range(n_seq)]
+    us = np.stack([uniforms(500 + i, n_new) for i in range(n_seq)], axis=1).astype(np.float64)     # [step][slot]
+    opt = SamplingOptions(temperature=0.9, top_p=0.9, repetition_penalty=1.1)
+    got = eng.generate(prompts, n_new, opt, draws=us, eos=SMALL_EOS)
+    for i in (0, 1, 17, 160, 299, 319):
+        ref = o.generate(prompts[i], n_new, 0.9, 0.9, 1.1, us=us[:, i].astype(np.float32), eos=SMALL_EOS)
+        assert np.array_equal(got[i], ref), i
