@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the token loop on B200: decode tokens/s against the HBM roofline.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c5] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
 
 Default workload (N=1): BASELINE config 2 -- the 100.3M model, batch 1, a prompt of 256 uniform
 random ids, 512 sampled decode steps (temperature 0.8, top-p 0.95, repetition penalty 1.15,
@@ -257,8 +257,8 @@ def run_c4(args):
         build.build()
     if world > 1:
         dist.barrier()
-    c5 = args.workload == "c5"
-    B, ITERS = (args.batch if not c5 or args.batch != 512 else 32 * world), 64
+    c5, c3 = args.workload == "c5", args.workload == "c3"
+    B, ITERS = (args.batch if not (c5 or c3) or args.batch != 512 else (32 * world if c5 else 64)), 64
     per = B // world
     # config 5: the scaled model (24 layers, d 1536, 24 heads of 64, FFN 4096), 32 sequences per GPU, prompts of 1024
     cfg = ModelConfig(num_layers=24, d_model=1536, num_heads=24, ffn_hidden=4096) if c5 else ModelConfig()
@@ -266,7 +266,8 @@ def run_c4(args):
     rng = np.random.default_rng(5 if c5 else 0)
     for name, shape in eng.param_infos():
         eng.set_param(name, rng.normal(0.0, 0.02, size=shape).astype(np.float32) if len(shape) == 2 else np.ones(shape, np.float32))
-    lens_all = np.full(B, 1024, np.int64) if c5 else 256 + (mt19937_raw(4, B) % np.uint32(1281)).astype(np.int64)
+    lens_all = (np.full(B, 1024, np.int64) if c5 else np.full(B, 512, np.int64) if c3 else
+                256 + (mt19937_raw(4, B) % np.uint32(1281)).astype(np.int64))
     lens = lens_all[rank * per:(rank + 1) * per]
     prompts = [prompt_ids(100 + rank * per + i, int(n)) for i, n in enumerate(lens)]
     opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
@@ -315,6 +316,7 @@ def run_c4(args):
             "per_iteration_ms": ms / n_iter, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 weights+KV, f32 accumulate", "data": "synthetic: N(0,0.02) weights, std::mt19937 ids and lengths",
             "config": {"workload": (f"BASELINE config 5: 0.73B model, batch {B} over {world} GPU(s), prompts of 1024, greedy decode, " if c5 else
+                                    f"BASELINE config 3: batch {B} over {world} GPU(s), prompts of 512, greedy decode, " if c3 else
                                     f"BASELINE config 4: batch {B} over {world} GPU(s), prompts uniform in [256,1536], greedy decode, ")
                                    + f"{ITERS} iterations per step", "mean_context_at_start": float(lens_all.mean()) + n_warm * ITERS,
                        "l2": "inputs larger than L2 (KV cache of tens of GB)"},
@@ -423,8 +425,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--decode-steps", type=int, default=N_NEW,
                     help="profiling only: shorter generations (the printed value is then not a benchmark figure)")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"],
-                    help="c2 (default, the headline), c4 = batch-512 decode, c5 = the 0.73B model at 32 sequences per GPU")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"],
+                    help="c2 (default, the headline), c3 = 64 sequences with prompts of 512, c4 = batch-512 decode, "
+                         "c5 = the 0.73B model at 32 sequences per GPU")
     ap.add_argument("--batch", type=int, default=512, help="c4 only: total sequences")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
@@ -436,7 +439,7 @@ def main():
         args.profile_only = False
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload in ("c4", "c5"):
+    elif args.workload in ("c3", "c4", "c5"):
         run_c4(args)
     else:
         if int(os.environ.get("WORLD_SIZE", "1")) > 1:
