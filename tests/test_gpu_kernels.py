@@ -106,3 +106,25 @@ def test_tensor_core_prefill_attention_matches_cuda_core_kernel(monkeypatch):
     ids = prompts[0]
     all_rows = eng.forward_logits(ids, 1, ids.size)[0]
     assert rel_err(all_rows, o.forward(ids, 1, ids.size)[0]) <= 2e-2
+
+
+def test_tensor_core_prefill_attention_full_context():
+    """A prompt that fills a 2048-position context (32 KV pages, 16 query tiles per head, several prefill chunks):
+    last-row logits and a few inner rows against the oracle; then three more tokens, which makes the window slide
+    (every token re-runs the last 2048 ids from position 0)."""
+    cfg = Config(vocab=512, context=2048, layers=1, d_model=128, heads=2, ffn=128)
+    o, eng = make_pair(cfg, seed=11, stddev=0.05, fp32=False, max_batch=1, via_checkpoint=False, max_chunk_tokens=768)
+    ids = prompt_ids(40, cfg.context, cfg.vocab)
+    from tests.helpers import rel_err
+    ref = o.forward(ids, 1, cfg.context)[0]
+    got = eng.forward_logits(ids, 1, cfg.context)[0]
+    for r in (0, 63, 64, 127, 128, 767, 768, 1500, 2047):
+        assert rel_err(got[r], ref[r]) <= 2e-2, r
+    from small_llm_b200 import SamplingOptions
+    out = eng.generate([ids], 3, SamplingOptions(temperature=0.0, repetition_penalty=1.0), None, eos=cfg.vocab + 5)[0]
+    assert out.size == cfg.context + 3
+    window = out[-cfg.context - 1:-1]                          # what the last step saw, positions restarting at 0
+    want = o.forward(window, 1, cfg.context)[0, -1]
+    # the last token is the arg-max of the oracle's logits for that window unless the top two are within the tolerance
+    top2 = np.sort(want)[-2:]
+    assert out[-1] == int(np.argmax(want)) or (top2[1] - top2[0]) <= 2e-2 * np.abs(want).max()
