@@ -183,8 +183,10 @@ int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n);
  * queries, d_tok_slot / d_tok_pos [n_tok] int32 (slot and position of each query; keys
  * 0..position of that slot's KV cache are attended), d_out [n_tok][d_model] fp32.  All four are
  * DEVICE pointers.  n_splits (1..32) blocks share each (token, head); with more than one, partial
- * results go through scratch memory that the engine allocated at creation.  The launch is
- * asynchronous on `stream` (a cudaStream_t as void*; NULL = the engine's stream). */
+ * results go through scratch memory that the engine allocated at creation.  More than 64 tokens need
+ * n_splits = 1 and take the page-streaming kernel that the engine uses at large batch (same arithmetic, K/V pages
+ * staged through shared memory).  The launch is asynchronous on `stream` (a cudaStream_t as void*; NULL = the
+ * engine's stream). */
 int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_tok_slot,
                        const int32_t* d_tok_pos, uint32_t n_splits, float* d_out, void* stream);
 
