@@ -173,6 +173,38 @@ public:
         return logits;
     }
 
+    // ops::cross_entropy(forward(token_ids), targets, num_valid) (src/ops/cross_entropy.cpp:14-54) without moving the
+    // logits off the device; targets are ids, negative = position ignored, num_valid 0 = mean over all positions.
+    // An extension: what a perplexity check of a checkpoint needs (exp of the returned loss).
+    float evalLoss(const std::vector<uint32_t>& token_ids, const std::vector<int32_t>& targets, size_t batch_size, size_t seq_len,
+                   size_t num_valid = 0) {
+        if (token_ids.size() != batch_size * seq_len || targets.size() != token_ids.size())
+            throw std::invalid_argument("Model::evalLoss: token_ids and targets must hold batch_size * seq_len entries");
+        if (seq_len > config_.context_length)
+            throw std::invalid_argument("Model::forward: seq_len exceeds context_length");
+        sllm_engine* e = engine();
+        const size_t group = options_.max_batch ? options_.max_batch : 1;
+        if (batch_size <= group) {
+            float loss = 0.f;
+            sllm_detail::check(sllm_eval_loss(e, token_ids.data(), targets.data(), batch_size, seq_len, num_valid, &loss), e);
+            return loss;
+        }
+        // more rows than sequence slots: per-group sums of the counted positions, recombined in double
+        double total = 0.0;
+        size_t counted = 0;
+        for (size_t b0 = 0; b0 < batch_size; b0 += group) {
+            const size_t nb = std::min(group, batch_size - b0);
+            size_t n = 0;
+            for (size_t i = b0 * seq_len; i < (b0 + nb) * seq_len; ++i) n += targets[i] >= 0;
+            if (n == 0) continue;
+            float loss = 0.f;
+            sllm_detail::check(sllm_eval_loss(e, token_ids.data() + b0 * seq_len, targets.data() + b0 * seq_len, nb, seq_len, n, &loss), e);
+            total += (double)loss * (double)n;
+            counted += n;
+        }
+        return static_cast<float>(total / static_cast<double>(num_valid ? num_valid : batch_size * seq_len));
+    }
+
     // every tensor in registry order; writing through Param::value takes effect at the next
     // forward / generate (or at refresh_bf16_weights())
     std::vector<Param> parameters() {

@@ -36,6 +36,13 @@ int main(int argc, char** argv) {
     out.write(reinterpret_cast<const char*>(&n), 8);
     out.write(reinterpret_cast<const char*>(logits.data()), n * 4);
 
+    std::vector<int32_t> targets(ids.size());
+    for (size_t i = 0; i < ids.size(); ++i) targets[i] = (i % 5 == 0) ? -1 : (int32_t)ids[(i + 1) % ids.size()];
+    size_t n_valid = 0;
+    for (int32_t v : targets) n_valid += v >= 0;
+    const float loss = model.evalLoss(ids, targets, 2, 37, n_valid);       // two rows on an engine with one slot: two groups
+    out.write(reinterpret_cast<const char*>(&loss), 4);
+
     Inference inf(model, tok);
     SamplingOptions opt; opt.temperature = 0.8f; opt.top_p = 0.9f; opt.repetition_penalty = 1.2f; opt.seed = 77;
     std::vector<uint32_t> prompt(ids.begin(), ids.begin() + 21);

@@ -37,10 +37,14 @@ def test_cpp_facade_on_gpu_matches_oracle(tmp_path):
     ids = np.array([(i * 7919 + 13) % 500 for i in range(2 * 37)], dtype=np.uint32)
     with open(res, "rb") as f:
         logits = _read(f, np.float32).reshape(2, 37, cfg.vocab)
+        loss = float(np.frombuffer(f.read(4), dtype=np.float32)[0])
         sampled = _read(f, np.uint32)
         reply1 = _read(f, np.uint32)
         reply2 = _read(f, np.uint32)
     assert rel_err(logits, o.forward(ids, 2, 37)) <= 2e-5                      # fp32 weights
+    from oracle.binding import cross_entropy
+    targets = np.array([-1 if i % 5 == 0 else int(ids[(i + 1) % ids.size]) for i in range(ids.size)], dtype=np.int32)
+    assert abs(loss - cross_entropy(o.forward(ids, 2, 37).reshape(74, cfg.vocab), targets, int((targets >= 0).sum()))) <= 2e-5
     ref = o.generate(ids[:21], 30, 0.8, 0.9, 1.2, seed=77, eos=eos)
     assert np.array_equal(sampled, ref)
     user, asst, end = eos + 1, eos + 2, eos + 3
