@@ -7,14 +7,16 @@
 //                           P = exp(S*scale - max) as bf16 in shared memory, row sums / maxima in registers
 //                           PV = P V         tcgen05.mma, 128 x 64 x 64
 //                           O = O * corr + PV  in registers (one thread owns one query row = one TMEM lane)
-// Operands in shared memory are K-major with the 128-byte swizzle: K pages come in by TMA over the whole KV pool
-// (a [rows][64] bf16 tensor), V pages by a bulk copy and are transposed to [dim][key] by four warps, Q (fp32 from
-// the projection) and P are written by the threads themselves in the swizzled layout.
-// Warps: 0 = copy producer, 1 = MMA issuer and TMEM owner, 2-5 = softmax (TMEM lane quarters 2,3,0,1); the softmax
-// warps also transpose the next page's V while the PV product of this page runs.  S is double-buffered in TMEM so that
-// S of the next page is computed while the softmax of this one runs.  192 threads at <= 168 registers and 97 KB of
-// shared memory: two blocks per SM, which overlap each other's dependency chains.  Every mbarrier wait is bounded
-// (two seconds), as in gemm_tc.cuh.
+// Operands in shared memory carry the 128-byte swizzle.  K and V pages come in by TMA over the whole KV pool (a
+// [rows][64] bf16 tensor) exactly as they lie in the cache, [key][dim]: for S the K page is the K-major B operand
+// (dim is the contraction), for PV the V page is the MN-major B operand (key is the contraction, dim contiguous), so
+// nothing is transposed.  Q (fp32 from the projection) and P are written by the threads themselves in the swizzled
+// K-major layout.  exp(x) is evaluated as exp2(x * log2 e); the causal mask is applied only on pages that reach the
+// tile's first query.
+// Warps: 0 = copy producer, 1 = MMA issuer and TMEM owner, 2-5 = softmax (TMEM lane quarters 2,3,0,1).  S is
+// double-buffered in TMEM so that S of the next page is computed while the softmax of this one runs.  192 threads at
+// <= 168 registers and 81 KB of shared memory: two blocks per SM, which overlap each other's dependency chains.
+// Every mbarrier wait is bounded (two seconds), as in gemm_tc.cuh.
 #pragma once
 #include "attn_stream.cuh"
 #include "gemm_tc.cuh"
@@ -39,8 +41,7 @@ struct AttnPtArgs {
 
 constexpr size_t attn_prefill_tc_smem() {
     return 1024 + (size_t)kPtQ * 128                       // Q
-           + (size_t)kPtStages * kPtPageBytes * 2          // K stages, raw V stages
-           + 2 * (size_t)kPtPageBytes                      // transposed V, two buffers
+           + (size_t)kPtStages * kPtPageBytes * 2          // K stages, V stages
            + (size_t)kPtQ * 128                            // P
            + 256;                                          // barriers, TMEM slot
 }
@@ -61,13 +62,11 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + kPtQ * 128;
-    uint8_t* sVraw = sK + kPtStages * kPtPageBytes;
-    uint8_t* sVt = sVraw + kPtStages * kPtPageBytes;
-    uint8_t* sP = sVt + 2 * kPtPageBytes;
+    uint8_t* sV = sK + kPtStages * kPtPageBytes;
+    uint8_t* sP = sV + kPtStages * kPtPageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPtQ * 128);
     // barrier indices
-    enum { K_FULL = 0, V_FULL = 3, K_FREE = 6, V_FREE = 9, S_READY = 12, S_FREE = 14, VT_READY = 16, P_READY = 18,
-           PV_READY = 19, N_BARS = 20 };
+    enum { K_FULL = 0, V_FULL = 3, K_FREE = 6, V_FREE = 9, S_READY = 12, S_FREE = 14, P_READY = 16, PV_READY = 17, N_BARS = 18 };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     const uint32_t bar0 = smem_u32(bars);
     auto B = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -78,8 +77,8 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
     const int D = a.m.D;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 3; ++i) { mbar_init(B(K_FULL + i), 1); mbar_init(B(V_FULL + i), 1); mbar_init(B(K_FREE + i), 1); mbar_init(B(V_FREE + i), 4); }
-        for (int i = 0; i < 2; ++i) { mbar_init(B(S_READY + i), 1); mbar_init(B(S_FREE + i), 4); mbar_init(B(VT_READY + i), 4); }
+        for (int i = 0; i < 3; ++i) { mbar_init(B(K_FULL + i), 1); mbar_init(B(V_FULL + i), 1); mbar_init(B(K_FREE + i), 1); mbar_init(B(V_FREE + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(B(S_READY + i), 1); mbar_init(B(S_FREE + i), 4); }
         mbar_init(B(P_READY), 4); mbar_init(B(PV_READY), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -127,8 +126,7 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
                 mbar_expect_tx(B(K_FULL + s), kPtPageBytes);
                 tma_load_2d(smem_u32(sK + s * kPtPageBytes), &map_kv, 0, (int)row, B(K_FULL + s));
                 mbar_expect_tx(B(V_FULL + s), kPtPageBytes);
-                bulk_g2s(smem_u32(sVraw + s * kPtPageBytes), kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, page, 1, head, 0), kPtPageBytes,
-                         B(V_FULL + s));
+                tma_load_2d(smem_u32(sV + s * kPtPageBytes), &map_kv, 0, (int)(row + (long long)a.m.H * kPage), B(V_FULL + s));
             }
         }
     } else if (warp == 1) {
@@ -150,15 +148,18 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
             ok = issue_qk(0);
             for (int i = 0; i < n_pages && ok; ++i) {
                 if (i + 1 < n_pages) { ok = issue_qk(i + 1); if (!ok) break; }
-                const int b = i & 1;
-                ok = mbar_wait(B(P_READY), i & 1, a.status, 35) && mbar_wait(B(VT_READY + b), (i >> 1) & 1, a.status, 36);
+                const int sv_ = i % kPtStages;
+                ok = mbar_wait(B(P_READY), i & 1, a.status, 35) && mbar_wait(B(V_FULL + sv_), (i / kPtStages) & 1, a.status, 36);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t pa = smem_u32(sP), vb = smem_u32(sVt + b * kPtPageBytes);
+                // V page as it lies in the cache, [key][dim]: the B operand in MN-major form (dim contiguous), 16 keys
+                // (two 8-row groups of 1024 bytes) per MMA
+                const uint32_t pa = smem_u32(sP), vb = smem_u32(sV + sv_ * kPtPageBytes);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    tc_mma_bf16(tmem + 128u, tc_smem_desc(pa + k * 32), tc_smem_desc(vb + k * 32), idesc, k != 0);
+                    tc_mma_bf16(tmem + 128u, tc_smem_desc(pa + k * 32), tc_smem_desc(vb + k * 2048), idesc | (1u << 16), k != 0);
                 tc_commit(B(PV_READY));
+                tc_commit(B(V_FREE + sv_));
             }
         }
     } else {
@@ -171,37 +172,20 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
 #pragma unroll
         for (int d = 0; d < 64; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
-        const int tt = threadIdx.x - 64, h = tt & 63, half = tt >> 6;
-        // page [key][dim] -> [dim][key], K-major swizzled, into buffer i & 1.  The buffer was last read by the PV
-        // product of page i - 2, whose completion this thread has already waited for.
-        auto transpose_v = [&](int i) -> bool {
-            const int s = i % kPtStages;
-            bool good = mbar_wait(B(V_FULL + s), (i / kPtStages) & 1, a.status, 39);
-            good = __all_sync(0xffffffffu, good);
-            if (!good) return false;
-            const unsigned short* src = reinterpret_cast<const unsigned short*>(sVraw + s * kPtPageBytes) + (half * 32) * 64 + h;
-            uint8_t* dst = sVt + (i & 1) * kPtPageBytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t lo = src[(c * 8 + 2 * e) * 64], hi = src[(c * 8 + 2 * e + 1) * 64];
-                    w[e] = lo | (hi << 16);
-                }
-                *reinterpret_cast<uint4*>(dst + sw128(h, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(B(VT_READY + (i & 1))); mbar_arrive(B(V_FREE + s)); }
-            return true;
-        };
-        ok = transpose_v(0);
+        const float sl2 = a.m.scale * 1.4426950408889634f;
+#ifdef SLLM_TIMELINE
+        unsigned long long tl_loc[48]; int tl_n = 0;
+#define PT_LOC() do { if (tl_n < 48) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); tl_loc[tl_n++] = t_; } } while (0)
+#else
+#define PT_LOC()
+#endif
+        PT_LOC();
         for (int i = 0; i < n_pages && ok; ++i) {
             const int b = i & 1;
             ok = mbar_wait(B(S_READY + b), (i >> 1) & 1, a.status, 37);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            PT_LOC();
             tc_fence_after();
             uint32_t sv[64];
             tc_ld32(lane_addr + (uint32_t)(b * 64), sv);
@@ -209,25 +193,37 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(B(S_FREE + b));
+            // scores in units of log2(e): exp(x) = exp2(x * log2 e), one multiply and one ex2 per element
             const int kbase = i * kPage;
-            float mx = -INFINITY;
+            float mxp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four interleaved chains instead of one of 64
+            if (kbase + kPage - 1 <= t.pos0) {                   // page entirely before the tile's first query: no mask
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                const float s = (kbase + j <= qpos) ? __uint_as_float(sv[j]) * a.m.scale : -INFINITY;
-                sv[j] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int j = 0; j < 64; ++j) {
+                    const float s = __uint_as_float(sv[j]) * sl2;
+                    sv[j] = __float_as_uint(s);
+                    mxp[j & 3] = fmaxf(mxp[j & 3], s);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const float s = (kbase + j <= qpos) ? __uint_as_float(sv[j]) * sl2 : -INFINITY;
+                    sv[j] = __float_as_uint(s);
+                    mxp[j & 3] = fmaxf(mxp[j & 3], s);
+                }
             }
+            const float mx = fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3]));
             const float m_new = fmaxf(m_run, mx);              // finite from the first page on: key 0 is never masked
-            const float corr = expf(m_run - m_new);
+            const float corr = exp2f(m_run - m_new);
             m_run = m_new;
-            float sum = 0.f;
+            float sump[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int j = 0; j < 64; j += 2) {
-                const float p0 = expf(__uint_as_float(sv[j]) - m_new), p1 = expf(__uint_as_float(sv[j + 1]) - m_new);
-                sum += p0 + p1;
+                const float p0 = exp2f(__uint_as_float(sv[j]) - m_new), p1 = exp2f(__uint_as_float(sv[j + 1]) - m_new);
+                sump[(j >> 1) & 3] += p0 + p1;
                 pk[j >> 1] = pack_bf16(p0, p1);
             }
+            const float sum = (sump[0] + sump[1]) + (sump[2] + sump[3]);
             l_run = l_run * corr + sum;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
@@ -236,16 +232,26 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
             tc_fence_before();                                   // the PV loads of the previous page are done before the next PV may start
             __syncwarp();
             if (lane == 0) mbar_arrive(B(P_READY));
-            if (i + 1 < n_pages && !transpose_v(i + 1)) { ok = false; break; }   // while the PV product of this page runs
+            PT_LOC();
+            PT_LOC();
             ok = mbar_wait(B(PV_READY), i & 1, a.status, 38);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            PT_LOC();
             tc_fence_after();
             tc_ld32(lane_addr + 128u, sv);
             tc_ld32(lane_addr + 160u, sv + 32);
 #pragma unroll
             for (int d = 0; d < 64; ++d) o[d] = o[d] * corr + __uint_as_float(sv[d]);
         }
+#ifdef SLLM_TIMELINE
+        PT_LOC();
+        if (threadIdx.x == 64 && blockIdx.x == 3 && blockIdx.y == 0) {
+            const unsigned int i0 = atomicAdd(&g_tl_n, (unsigned int)tl_n);
+            for (int i = 0; i < tl_n; ++i)
+                if (i0 + i < (1u << 15)) { g_tl_buf[2 * (i0 + i)] = 800 + i; g_tl_buf[2 * (i0 + i) + 1] = tl_loc[i]; }
+        }
+#endif
         if (ok && r < t.n_q) {
             const float inv = 1.0f / l_run;
             float* dst = a.out + (size_t)(t.tok_begin + r) * D + head * 64;

@@ -98,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
         if (t0 == 0) t0 = now;
         else if (now - t0 > kWaitLimitNs) break;
-        __nanosleep(128);
+        __nanosleep(32);
     }
     atomicExch(status, code);
     return false;
