@@ -1245,6 +1245,9 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
         if (!rc) rc = make_map(e, &e->map_head, e->emb_w, V, D, kTcBM);
         // tensor-core prefill attention: head_dim 64, the pool as one [rows][64] tensor whose rows fit a TMA coordinate
         const unsigned long long kv_rows = (unsigned long long)L * (unsigned long long)e->n_pages * 2ull * H * kPage;
+        if (!rc && kv_rows >= (1ull << 32)) {      // the projection epilogue addresses KV rows with 32-bit indices
+            e->err = "KV pool has more than 2^32 rows of head_dim elements"; rc = SLLM_ERR_CAPACITY;
+        }
         if (!rc && hd == 64 && kv_rows < (1ull << 31) && std::getenv("SLLM_NO_ATTN_TC") == nullptr) {
             rc = make_map(e, &e->map_kv, e->kv_pool, kv_rows, 64, kPage);
             if (!rc && cudaFuncSetAttribute(k_attn_prefill_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,

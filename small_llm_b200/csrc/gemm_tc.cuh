@@ -278,8 +278,10 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
         // While the tensor cores work, each epilogue warp fetches the positions and KV pages of its tokens into
         // its own shared-memory copy, and the operands of its first column chunk that do not depend on the
         // accumulator (rotation factors, residual values), so that little is left to wait for afterwards.
+        // per token: its position (for the rotation factors) and the row of the KV pool, in units of head_dim
+        // elements, at which head 0's K entry of that position lies
         int* my_pos = tok_meta + ew * 2 * HALF;
-        int* my_page = my_pos + HALF;
+        uint32_t* my_kvrow = reinterpret_cast<uint32_t*>(my_pos + HALF);
         if (MODE == kModeQKV) {
             for (int j = lane; j < HALF; j += 32) {
                 const int tok = t0 + cbeg + j;
@@ -288,10 +290,15 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
                     pos = a.pass.tok_pos[tok];
                     page = a.kv.block_table[(size_t)a.pass.tok_slot[tok] * a.kv.pages_per_seq + pos / kPage];
                 }
-                my_pos[j] = pos; my_page[j] = page;
+                my_pos[j] = pos;
+                my_kvrow[j] = (uint32_t)((((unsigned long long)a.layer * a.kv.n_pages + page) * 2 * a.m.H) * kPage + pos % kPage);
             }
             __syncwarp();
         }
+        // this lane's constant part of the addresses it stores to
+        float* const q_lane = a.out + col;
+        __nv_bfloat16* const kv_lane = reinterpret_cast<__nv_bfloat16*>(a.kv.pool) + d;
+        const uint32_t kv_lane_row = (uint32_t)(((which > 0 ? which - 1 : 0) * a.m.H + head) * kPage);
         float2 cs[MODE == kModeQKV ? CW : 1];
         float xv[MODE == kModeResidual ? CW : 1];
         const bool scaled = (MODE == kModeQKV || MODE == kModeGateUp) && a.ss_in != nullptr;
@@ -415,13 +422,8 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
                 for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c0 + j;
                     if (!row_ok || tok >= a.n_tok) continue;
-                    if (which == 0) {
-                        a.out[(size_t)tok * D + col] = r[j];
-                    } else {
-                        const int pos = my_pos[c0 - cbeg + j];
-                        kv_ptr<__nv_bfloat16>(a.kv, a.m, a.layer, my_page[c0 - cbeg + j], which - 1, head, pos % kPage)[d] =
-                            __float2bfloat16_rn(r[j]);
-                    }
+                    if (which == 0) q_lane[(uint32_t)tok * (uint32_t)D] = r[j];
+                    else kv_lane[(size_t)(my_kvrow[c0 - cbeg + j] + kv_lane_row) * (uint32_t)hd] = __float2bfloat16_rn(r[j]);
                 }
             }
         }
