@@ -396,16 +396,21 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
                     if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = __uint_as_float(v[j]);
                 }
             } else if (MODE == kModeGateUp) {
-                // (gate, up) sit in adjacent lanes; every lane evaluates the same branch-free expression so that
-                // the columns overlap in the pipeline, and the even lanes store
-                const bool store_lane = row_ok && (row & 1) == 0;
+                // (gate, up) of a hidden unit sit in adjacent lanes.  Two columns per step: the even lane finishes
+                // column j (its own gate, the neighbour's up), the odd lane column j + 1 (the neighbour's gate, its
+                // own up), so one exchange and one SiLU serve two tokens and every lane's result is stored
+                const bool odd = (row & 1) != 0;
+                __nv_bfloat16* const h_lane = a.out_bf16 + (row >> 1);
+                const uint32_t h_stride = (uint32_t)(a.R / 2);
 #pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
-                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
-                    const float hval = __fdividef(acc, 1.0f + __expf(-acc)) * other;
-                    const int tok = t0 + c0 + j;
-                    if (store_lane && tok < a.n_tok) a.out_bf16[(size_t)tok * (a.R / 2) + (row >> 1)] = __float2bfloat16_rn(hval);
+                for (int j = 0; j < CW; j += 2) {
+                    const float a0 = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
+                    const float a1 = __uint_as_float(v[j + 1]) * my_rs[c0 - cbeg + j + 1];
+                    const float recv = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+                    const float g = odd ? recv : a0, u = odd ? a1 : recv;
+                    const float hval = __fdividef(g, 1.0f + __expf(-g)) * u;
+                    const int tok = t0 + c0 + j + (odd ? 1 : 0);
+                    if (row_ok && tok < a.n_tok) h_lane[(size_t)((uint32_t)tok * h_stride)] = __float2bfloat16_rn(hval);
                 }
             } else {
                 // RoPE pairs sit in adjacent lanes
