@@ -295,7 +295,9 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
             }
             __syncwarp();
         }
-        // this lane's constant part of the addresses it stores to
+        // this lane's constant part of the addresses it loads from and stores to
+        float* const x_lane = a.out + row;                       // Residual / Head: [tok][R] fp32
+        __nv_bfloat16* const xn_lane = a.xn_out + row;
         float* const q_lane = a.out + col;
         __nv_bfloat16* const kv_lane = reinterpret_cast<__nv_bfloat16*>(a.kv.pool) + d;
         const uint32_t kv_lane_row = (uint32_t)(((which > 0 ? which - 1 : 0) * a.m.H + head) * kPage);
@@ -335,7 +337,7 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c + j;
-                    xv[j] = (row_ok && tok < a.n_tok) ? a.out[(size_t)tok * a.R + row] : 0.f;
+                    xv[j] = (row_ok && tok < a.n_tok) ? x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] : 0.f;
                 }
             }
         };
@@ -377,8 +379,8 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
                 for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c0 + j;
                     if (row_ok && tok < a.n_tok) {
-                        a.out[(size_t)tok * a.R + row] = r[j];
-                        if (a.gain_next) a.xn_out[(size_t)tok * a.R + row] = __float2bfloat16_rn(r[j] * gnext);
+                        x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = r[j];
+                        if (a.gain_next) xn_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = __float2bfloat16_rn(r[j] * gnext);
                     }
                 }
                 if (a.gain_next) {                               // uniform over the grid
@@ -393,7 +395,7 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
                     const int tok = t0 + c0 + j;
-                    if (row_ok && tok < a.n_tok) a.out[(size_t)tok * a.R + row] = __uint_as_float(v[j]);
+                    if (row_ok && tok < a.n_tok) x_lane[(size_t)tok * a.R] = __uint_as_float(v[j]);
                 }
             } else if (MODE == kModeGateUp) {
                 // (gate, up) of a hidden unit sit in adjacent lanes.  Two columns per step: the even lane finishes
