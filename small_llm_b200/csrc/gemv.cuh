@@ -1,4 +1,5 @@
-// Weight-streaming projections for small token counts (decode at small batch).
+// Weight-streaming projections: every pass with fp32 weights, the head of the one-token decode step, and bf16 passes
+// when the driver offers no tensor-map encoder (bf16 passes of two and more tokens otherwise take gemm_tc.cuh).
 //
 // Every projection of the model is y[t][r] = sum_k x[t][k] * W[r][k] with W stored row-per-output
 // ("[R][K]", the transpose of the reference's x@W matrices, re-laid-out once at load time), so a
