@@ -985,6 +985,10 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         CU(cudaMemcpyAsync(e->d_tok_id, c_id.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         CU(cudaMemcpyAsync(e->d_tok_slot, c_slot.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         CU(cudaMemcpyAsync(e->d_tok_pos, c_pos.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
+        // the attention grid takes its tiles in this order: the ones with the most KV pages first, so that the last
+        // wave of blocks is the shortest
+        std::stable_sort(c_tiles.begin(), c_tiles.end(),
+                         [](const PfTile& x, const PfTile& y) { return x.pos0 + x.n_q > y.pos0 + y.n_q; });
         CU(cudaMemcpyAsync(e->d_tiles, c_tiles.data(), c_tiles.size() * sizeof(PfTile), cudaMemcpyHostToDevice, e->stream));
         PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n, e->d_tiles, (int)c_tiles.size()};
         e->prefill_tokens += (uint64_t)n;
