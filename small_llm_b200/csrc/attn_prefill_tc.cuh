@@ -173,19 +173,11 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
         for (int d = 0; d < 64; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         const float sl2 = a.m.scale * 1.4426950408889634f;
-#ifdef SLLM_TIMELINE
-        unsigned long long tl_loc[48]; int tl_n = 0;
-#define PT_LOC() do { if (tl_n < 48) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); tl_loc[tl_n++] = t_; } } while (0)
-#else
-#define PT_LOC()
-#endif
-        PT_LOC();
         for (int i = 0; i < n_pages && ok; ++i) {
             const int b = i & 1;
             ok = mbar_wait(B(S_READY + b), (i >> 1) & 1, a.status, 37);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            PT_LOC();
             tc_fence_after();
             uint32_t sv[64];
             tc_ld32(lane_addr + (uint32_t)(b * 64), sv);
@@ -232,26 +224,15 @@ __global__ void __launch_bounds__(kPtThreads, 2) k_attn_prefill_tc(const __grid_
             tc_fence_before();                                   // the PV loads of the previous page are done before the next PV may start
             __syncwarp();
             if (lane == 0) mbar_arrive(B(P_READY));
-            PT_LOC();
-            PT_LOC();
             ok = mbar_wait(B(PV_READY), i & 1, a.status, 38);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            PT_LOC();
             tc_fence_after();
             tc_ld32(lane_addr + 128u, sv);
             tc_ld32(lane_addr + 160u, sv + 32);
 #pragma unroll
             for (int d = 0; d < 64; ++d) o[d] = o[d] * corr + __uint_as_float(sv[d]);
         }
-#ifdef SLLM_TIMELINE
-        PT_LOC();
-        if (threadIdx.x == 64 && blockIdx.x == 3 && blockIdx.y == 0) {
-            const unsigned int i0 = atomicAdd(&g_tl_n, (unsigned int)tl_n);
-            for (int i = 0; i < tl_n; ++i)
-                if (i0 + i < (1u << 15)) { g_tl_buf[2 * (i0 + i)] = 800 + i; g_tl_buf[2 * (i0 + i) + 1] = tl_loc[i]; }
-        }
-#endif
         if (ok && r < t.n_q) {
             const float inv = 1.0f / l_run;
             float* dst = a.out + (size_t)(t.tok_begin + r) * D + head * 64;
