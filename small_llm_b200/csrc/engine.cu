@@ -48,10 +48,10 @@ struct ParamSlot {
 };
 
 struct GraphKey {
-    int n_slots; float t, p, pen; uint32_t eos; long long stop; int seeded; int stride; const void* draws;
+    int n_slots; float t, p, pen; uint32_t eos; long long stop; int seeded; int stride; const void* draws; int iters;
     bool operator<(const GraphKey& o) const {
-        return std::tie(n_slots, t, p, pen, eos, stop, seeded, stride, draws) <
-               std::tie(o.n_slots, o.t, o.p, o.pen, o.eos, o.stop, o.seeded, o.stride, o.draws);
+        return std::tie(n_slots, t, p, pen, eos, stop, seeded, stride, draws, iters) <
+               std::tie(o.n_slots, o.t, o.p, o.pen, o.eos, o.stop, o.seeded, o.stride, o.draws, o.iters);
     }
 };
 
@@ -738,8 +738,11 @@ int enqueue_iteration(sllm_engine* e, const SampleArgs& s) {
     return run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, true);
 }
 
-int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* out) {
+// A graph of `iters` consecutive decode iterations: inside it the head of one iteration and the sampler of the next
+// are joined by a programmatic-dependent-launch edge like every other pair of kernels, which a graph boundary is not.
+int get_iteration_graph(sllm_engine* e, const SampleArgs& s, int iters, cudaGraphExec_t* out) {
     GraphKey k{};
+    k.iters = iters;
     k.n_slots = s.n_slots; k.t = s.temperature; k.p = s.top_p; k.pen = s.penalty; k.eos = s.eos; k.stop = s.stop_token;
     k.seeded = s.seeded; k.stride = s.draws_stride; k.draws = s.draws;
     auto it = e->graphs.find(k);
@@ -749,7 +752,8 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, cudaGraphExec_t* ou
     cudaGraph_t g = nullptr;
     const uint64_t before = e->launches;
     CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_iteration(e, s);
+    int rc = SLLM_OK;
+    for (int i = 0; i < iters && !rc; ++i) rc = enqueue_iteration(e, s);
     cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
     e->iter_launches = (int)(e->launches - before);
     e->launches = before;
@@ -1629,28 +1633,53 @@ int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n) {
 static int decode_loop_impl(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* d_draws, int stride,
                             int seeded, bool last_pass, bool* all_done_out) {
     SampleArgs s = make_sample_args(e, opt, e->n_live, d_draws, stride, seeded);
-    cudaGraphExec_t ge = nullptr;
+    cudaGraphExec_t ge = nullptr, ge_multi = nullptr;
+    constexpr uint64_t kMulti = 8, check_every = 64;           // kMulti divides check_every
+    int launches_one = 0, launches_multi = 0;
     { int rc = refresh_attn_order(e); if (rc) return rc; }
-    if (e->opt.use_graph) { int rc = get_iteration_graph(e, s, &ge); if (rc) return rc; }
-    const uint64_t check_every = 64;
-    for (uint64_t i = 0; i < n_steps; ++i) {
-        int rc = grow_for_step(e);
+    if (e->opt.use_graph) {
+        int rc = get_iteration_graph(e, s, 1, &ge);
         if (rc) return rc;
-        const bool final_one = (i + 1 == n_steps) && !last_pass;
-        if (final_one) {
-            rc = launch_sampler(e, s, false);
+        launches_one = launches_per_iteration(e);
+        if (n_steps > kMulti) {
+            rc = get_iteration_graph(e, s, (int)kMulti, &ge_multi);
             if (rc) return rc;
-        } else if (ge) {
-            CU(cudaGraphLaunch(ge, e->stream));
-            e->launches += launches_per_iteration(e);
-        } else {
-            rc = enqueue_iteration(e, s);
+            launches_multi = launches_per_iteration(e);
+            // inserting a graph may have emptied the cache (it is cleared when it grows past 32 entries)
+            rc = get_iteration_graph(e, s, 1, &ge);
             if (rc) return rc;
         }
-        e->decode_steps += final_one ? 0 : 1;
-        if ((i + 1) % check_every == 0 || i + 1 == n_steps) {
+    }
+    const uint64_t full_steps = last_pass ? n_steps : n_steps - 1;     // the last step of a generate call only samples
+    uint64_t i = 0;
+    while (i < n_steps) {
+        uint64_t done = 1;
+        if (ge_multi && i % kMulti == 0 && i + kMulti <= full_steps) {
+            for (uint64_t k = 0; k < kMulti; ++k) { int rc = grow_for_step(e); if (rc) return rc; }
+            CU(cudaGraphLaunch(ge_multi, e->stream));
+            e->launches += launches_multi;
+            e->decode_steps += kMulti;
+            done = kMulti;
+        } else {
+            int rc = grow_for_step(e);
+            if (rc) return rc;
+            const bool final_one = (i + 1 == n_steps) && !last_pass;
+            if (final_one) {
+                rc = launch_sampler(e, s, false);
+                if (rc) return rc;
+            } else if (ge) {
+                CU(cudaGraphLaunch(ge, e->stream));
+                e->launches += launches_one;
+            } else {
+                rc = enqueue_iteration(e, s);
+                if (rc) return rc;
+            }
+            e->decode_steps += final_one ? 0 : 1;
+        }
+        i += done;
+        if (i % check_every == 0 || i == n_steps) {
             bool all_done, nonfinite;
-            rc = check_finished_flags(e, &all_done, &nonfinite);
+            int rc = check_finished_flags(e, &all_done, &nonfinite);
             if (rc) return rc;
             if (nonfinite) return fail(e, SLLM_ERR_NONFINITE, "Inference::generate: all logits are non-finite");
             if (all_done_out) *all_done_out = all_done;
