@@ -6,8 +6,9 @@
  * with the reference's own names (ModelConfig, Model, Inference, SamplingOptions,
  * load_checkpoint_weights) are a header-only layer over these calls: include/small_llm.hpp.
  *
- * Threading: an engine belongs to one host thread and one GPU.  Several engines (one per
- * GPU, or several on one GPU) may live in one process.  There is no CPU fallback: every call
+ * Threading: an engine belongs to one host thread and one GPU: calls on one engine must be
+ * serialised by the caller (none of them locks).  Several engines (one per GPU, or several on one
+ * GPU) may live in one process, each driven by its own thread.  There is no CPU fallback: every call
  * that computes needs a CUDA device of compute capability 10.x and fails with
  * SLLM_ERR_CUDA otherwise.
  */
@@ -142,15 +143,25 @@ int sllm_truncate(sllm_engine* e, uint32_t slot, uint64_t n_tokens);
  * A slot stops after EOS or stop_token is appended or after max_new tokens.  When a slot holds more
  * than context_length tokens the window slides as in the reference (src/inference.cpp:40-48): each
  * further token re-runs the last context_length tokens with positions restarting at 0.  Prompts may be
- * longer than context_length for the same reason; a slot can hold 2 * context_length + 1 tokens. */
+ * longer than context_length for the same reason; a slot can hold 2 * context_length + 2 tokens, and a call
+ * whose prompt length + max_new_tokens exceeds that is refused with SLLM_ERR_CAPACITY. */
 int sllm_generate(sllm_engine* e, const uint32_t* prompt_ids, const uint32_t* prompt_lens, uint32_t n_seq,
                   uint64_t max_new_tokens, const sllm_sampling* opt, const double* draws,
                   uint32_t* out_tokens, uint64_t out_stride, uint64_t* out_lens);
 
-/* Device-resident variant used by benchmarks: the decode loop only, for slots already
- * prefilled; runs n_steps x (sample, decode step) without host round trips and returns after
- * the stream is idle.  draws_dev_index selects how draws are consumed as in sllm_generate. */
+/* The decode loop only, for slots already prefilled or assigned: runs n_steps x (sample, decode step)
+ * without host round trips and returns after the stream is idle.  draws (HOST memory, NULL when greedy):
+ * [n_steps][sllm_num_live(e)] doubles, draw[step][slot] feeds step `step` of that slot; the column count
+ * is the engine's live-slot range, parked slots included (their column is ignored).  At most
+ * 2 * context_length + 2 steps per call (the engine's draw buffer is sized once, at creation). */
 int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws);
+/* The same loop with one CUDA event between consecutive iterations: step_ms[i] (HOST memory, [n_steps]) receives
+ * the device time of iteration i in milliseconds -- the per-token latency samples a p50 / p95 is taken from.
+ * Each iteration is replayed as its own graph here (the untimed loop replays eight per graph), which adds a few
+ * microseconds per iteration.  At most 65536 steps per call. */
+int sllm_decode_loop_timed(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws, float* step_ms);
+/* Slots 0..sllm_num_live(e)-1 form the live range: the highest slot that holds a sequence, plus one. */
+uint32_t sllm_num_live(const sllm_engine* e);
 
 /* ops::cross_entropy(Model::forward(ids), targets, num_valid), src/ops/cross_entropy.cpp:14-54, without moving
  * the logits off the device: the mean over the counted positions of -logit[target] + log-sum-exp, per-row terms in
@@ -207,6 +218,25 @@ int sllm_k_attn_decode(sllm_engine* e, uint32_t layer, uint32_t n_tok, const flo
 int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q,
                               const int32_t* d_tok_slot, const int32_t* d_tok_pos, uint32_t n_splits, float* d_out,
                               void* stream);
+
+/* ---- the KV cache of one slot, from and to the host --------------------------------------------
+ * No counterpart in the reference (it keeps no KV cache; these rows are what its Attention::forward holds in k and
+ * v after split_heads and rope, src/nn/attention.cpp:68-77, for the slot's positions).  Rows are HOST memory,
+ * [n_pos][num_heads * head_dim] fp32 with head h in columns h * head_dim .., positions pos0 .. pos0 + n_pos - 1 of
+ * `layer`; the positions must lie inside the pages the slot already holds (it was prefilled or assigned at least
+ * that far).  Writing converts to the cache's element type (bf16 or fp32); reading converts back.  Uses: moving a
+ * prefix between engines, and checking the attention kernels against ops::attention on the same K and V. */
+int sllm_kv_write(sllm_engine* e, uint32_t layer, uint32_t slot, uint32_t pos0, uint32_t n_pos, const float* k_rows, const float* v_rows);
+int sllm_kv_read(sllm_engine* e, uint32_t layer, uint32_t slot, uint32_t pos0, uint32_t n_pos, float* k_rows, float* v_rows);
+
+/* ---- diagnostics ------------------------------------------------------------------------------ */
+/* No counterpart in the reference.  Every device-side wait of this library (mbarrier waits of the TMA / tcgen05
+ * pipelines) polls for a bounded time, then raises the engine's status word and lets its kernel return; the host
+ * reports SLLM_ERR_DEVICE_WAIT at its next synchronisation and the engine stays usable.  This entry point
+ * exercises exactly that path: it launches one thread that waits, for limit_us microseconds at most
+ * (1..100000), on a barrier that nothing arrives at, and returns what the host then sees --
+ * SLLM_ERR_DEVICE_WAIT.  Nothing faults, traps or spins without bound. */
+int sllm_k_wait_probe(sllm_engine* e, uint32_t limit_us);
 
 #ifdef __cplusplus
 }

@@ -516,8 +516,9 @@ public:
         std::vector<double> draws;
         if (opt.temperature > 0.0f) {                      // [step][slot], this slot's column filled
             std::mt19937_64 rng(opt.seed + turns_);
-            draws.assign(max_new_tokens * (slot_ + 1), 0.0);
-            for (size_t i = 0; i < max_new_tokens; ++i) draws[i * (slot_ + 1) + slot_] = std::generate_canonical<double, 53>(rng);
+            const size_t live = sllm_num_live(e);       // other sessions may hold higher slots of the same engine
+            draws.assign(max_new_tokens * live, 0.0);
+            for (size_t i = 0; i < max_new_tokens; ++i) draws[i * live + slot_] = std::generate_canonical<double, 53>(rng);
         }
         sllm_detail::check(sllm_decode_loop(e, max_new_tokens, &s, draws.empty() ? nullptr : draws.data()), e);
         ++turns_;

@@ -22,7 +22,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libsllm_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libsllm_ref.so")
 REF_FAST_SO = os.path.join(HERE, "_ref", "libsllm_ref_fast.so")
-REF_TREE = os.environ.get("SLLM_REF_DIR", "/root/reference")
+# Root of the small-llm tree: $SLLM_REF_DIR, else a checkout named "reference" beside this repository; empty when
+# neither exists (then the reference build is skipped and only its committed golden vectors are used).
+_SIBLING = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+REF_TREE = os.environ.get("SLLM_REF_DIR") or (_SIBLING if os.path.isdir(os.path.join(_SIBLING, "src")) else "")
 
 u32p = C.POINTER(C.c_uint32)
 u64p = C.POINTER(C.c_uint64)
@@ -43,7 +46,7 @@ def build_oracle(force: bool = False) -> str:
 
 def build_ref(force: bool = False) -> str | None:
     """Compile the reference's own sources where they lie; None when the tree is absent."""
-    if os.path.isdir(os.path.join(REF_TREE, "src")):
+    if REF_TREE and os.path.isdir(os.path.join(REF_TREE, "src")):
         shim = os.path.join(HERE, "ref_shim.cpp")
         if force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < os.path.getmtime(shim):
             subprocess.run(["make", "-C", HERE, "ref", f"REF={REF_TREE}"], check=True, capture_output=True)
@@ -290,7 +293,8 @@ class OracleSession:
 class RefModel:
     """The unmodified reference behind ref_shim.cpp (parity build by default)."""
 
-    def __init__(self, cfg: Config, fast: bool = False):
+    def __init__(self, cfg: Config, fast: bool = False, ctor_seed: int | None = None):
+        """ctor_seed: Tensor::seed(ctor_seed) before Model::Model, i.e. the reference's own initial weights."""
         path = REF_FAST_SO if fast else REF_SO
         if not os.path.exists(path):
             raise FileNotFoundError(path)
@@ -320,7 +324,12 @@ class RefModel:
         self.lib = lib
         self.cfg = cfg
         c = cfg.as_u64()
-        self.h = lib.ref_model_create(_ptr(c, u64p), cfg.theta, cfg.eps)
+        if ctor_seed is None:
+            self.h = lib.ref_model_create(_ptr(c, u64p), cfg.theta, cfg.eps)
+        else:
+            lib.ref_model_create_seeded.restype = C.c_void_p
+            lib.ref_model_create_seeded.argtypes = [u64p, C.c_float, C.c_float, C.c_uint32]
+            self.h = lib.ref_model_create_seeded(_ptr(c, u64p), cfg.theta, cfg.eps, ctor_seed)
         if not self.h:
             raise ValueError(lib.ref_last_error().decode())
 

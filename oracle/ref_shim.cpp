@@ -73,6 +73,12 @@ void* ref_model_create(const uint64_t* cfg, float theta, float eps) {
     try { return new Model(make_cfg(cfg, theta, eps)); }
     catch (const std::exception& e) { fail(e, 1); return nullptr; }
 }
+// The reference's own initialisation: Tensor::seed(seed), then Model::Model (src/model.cpp:15-29) draws every
+// matrix from the global generator in construction order.
+void* ref_model_create_seeded(const uint64_t* cfg, float theta, float eps, uint32_t seed) {
+    try { Tensor::seed(seed); return new Model(make_cfg(cfg, theta, eps)); }
+    catch (const std::exception& e) { fail(e, 1); return nullptr; }
+}
 void ref_model_destroy(void* m) { delete static_cast<Model*>(m); }
 
 // Benchmark initialisation: reseed the reference's global generator, then every matrix

@@ -69,7 +69,8 @@ ABI_SYMBOLS = [
     "sllm_param_info", "sllm_set_param", "sllm_load_checkpoint", "sllm_forward_logits", "sllm_reset",
     "sllm_prefill", "sllm_sample", "sllm_decode_step", "sllm_get_step_logits", "sllm_get_tokens",
     "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
-    "sllm_eval_loss", "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished",
+    "sllm_eval_loss", "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished", "sllm_num_live",
+    "sllm_k_wait_probe", "sllm_kv_write", "sllm_kv_read", "sllm_decode_loop_timed",
 ]
 
 
@@ -118,6 +119,12 @@ def load_library(path: str | None = None):
     lib.sllm_eval_loss.argtypes = [E, u32p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(C.c_float)]
     lib.sllm_slot_release.argtypes = [E, C.c_uint32]
     lib.sllm_get_finished.argtypes = [E, i32p, C.c_uint32]
+    lib.sllm_k_wait_probe.argtypes = [E, C.c_uint32]
+    lib.sllm_decode_loop_timed.argtypes = [E, C.c_uint64, C.POINTER(_Sampling), f64p, f32p]
+    lib.sllm_kv_write.argtypes = [E, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, f32p, f32p]
+    lib.sllm_kv_read.argtypes = [E, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, f32p, f32p]
+    lib.sllm_num_live.restype = C.c_uint32
+    lib.sllm_num_live.argtypes = [E]
     for fn in (lib.sllm_k_attn_decode, lib.sllm_k_attn_decode_static):
         fn.argtypes = [E, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     if path is None:
@@ -295,6 +302,17 @@ class Engine:
             dp = draws.ctypes.data_as(f64p)
         self._ck(self.lib.sllm_decode_loop(self.h, n_steps, C.byref(s), dp))
 
+    def decode_loop_timed(self, n_steps: int, opt: SamplingOptions, draws=None, eos: int = 32762) -> np.ndarray:
+        """decode_loop with a CUDA event per iteration; returns the device time of every iteration in ms."""
+        s = self._sampling(opt, eos)
+        dp = None
+        if draws is not None:
+            draws = np.ascontiguousarray(draws, dtype=np.float64)
+            dp = draws.ctypes.data_as(f64p)
+        out = np.zeros(n_steps, dtype=np.float32)
+        self._ck(self.lib.sllm_decode_loop_timed(self.h, n_steps, C.byref(s), dp, out.ctypes.data_as(f32p)))
+        return out
+
     # ---- token loop in one call -------------------------------------------------------------------
     def generate(self, prompts, max_new: int, opt: SamplingOptions, draws=None, eos: int = 32762):
         """prompts: list of id sequences.  draws: [max_new][n_seq] float64 or None (seeded mode).
@@ -339,6 +357,10 @@ class Engine:
     def slot_release(self, slot: int):
         self._ck(self.lib.sllm_slot_release(self.h, slot))
 
+    def num_live(self) -> int:
+        """Column count of the draw matrix sllm_decode_loop reads: highest slot that holds a sequence, plus one."""
+        return int(self.lib.sllm_num_live(self.h))
+
     def finished(self, n: int) -> np.ndarray:
         out = np.zeros(n, dtype=np.int32)
         self._ck(self.lib.sllm_get_finished(self.h, out.ctypes.data_as(C.POINTER(C.c_int32)), n))
@@ -349,6 +371,23 @@ class Engine:
         """Launches the flash-decode attention kernel alone; every d_* is a device address."""
         fn = self.lib.sllm_k_attn_decode_static if static_scratch else self.lib.sllm_k_attn_decode
         self._ck(fn(self.h, layer, n_tok, d_q, d_tok_slot, d_tok_pos, n_splits, d_out, stream or None))
+
+    def kv_write(self, layer: int, slot: int, pos0: int, k_rows, v_rows):
+        """K / V rows [n_pos][d_model] fp32 into the slot's cache at positions pos0.. of `layer`."""
+        k = np.ascontiguousarray(k_rows, dtype=np.float32)
+        v = np.ascontiguousarray(v_rows, dtype=np.float32)
+        assert k.shape == v.shape and k.shape[1] == self.config.d_model
+        self._ck(self.lib.sllm_kv_write(self.h, layer, slot, pos0, k.shape[0], k.ctypes.data_as(f32p), v.ctypes.data_as(f32p)))
+
+    def kv_read(self, layer: int, slot: int, pos0: int, n_pos: int):
+        k = np.empty((n_pos, self.config.d_model), dtype=np.float32)
+        v = np.empty_like(k)
+        self._ck(self.lib.sllm_kv_read(self.h, layer, slot, pos0, n_pos, k.ctypes.data_as(f32p), v.ctypes.data_as(f32p)))
+        return k, v
+
+    def wait_probe(self, limit_us: int):
+        """Diagnostic: one device thread waits limit_us on a barrier nobody arrives at; raises SllmError(ERR_DEVICE_WAIT)."""
+        self._ck(self.lib.sllm_k_wait_probe(self.h, limit_us))
 
     def stats(self) -> dict:
         s = _Stats()

@@ -46,7 +46,7 @@ class ContinuousBatcher:
 
         fill()
         while any(r is not None for r in slot_req):
-            live = max(s for s, r in enumerate(slot_req) if r is not None) + 1
+            live = eng.num_live()              # the engine reads draws as [steps][its live-slot range]
             steps = self.burst
             draws = None
             if sampled:

@@ -47,7 +47,7 @@ class ChatSession:
         n_before = self.eng.tokens(self.slot).size
         d = None
         if opt.temperature > 0.0:
-            live = self.slot + 1
+            live = self.eng.num_live()         # other sessions may hold higher slots of the same engine
             d = np.zeros((max_new_tokens, live), dtype=np.float64)
             d[:, self.slot] = np.asarray(draws, dtype=np.float64)[:max_new_tokens]
         self.eng.decode_loop(max_new_tokens, opt, d, eos=self.eos)

@@ -23,25 +23,8 @@ __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// false = gave up after two seconds
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        if (bar_try(bar, parity)) return true;
-        if (i < 64) continue;
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > 2000000000ull) return false;
-        __nanosleep(64);
-    }
-}
+// false = gave up (the engine's wait limit, see common.cuh)
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) { return mbar_wait_bounded(bar, parity, c_wait_limit_ns); }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");

@@ -59,6 +59,34 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- bounded mbarrier wait: the one wait loop of every kernel in this library ------------------------------
+// A wait polls for kWaitLimitNs of wall-clock time at most (c_wait_limit_ns, two seconds unless the engine was
+// created with SLLM_WAIT_LIMIT_MS set); then it gives up and the caller raises the engine's status word, leaves
+// its loops, frees what it holds and returns, so that a lost signal ends as an error code on the host
+// (SLLM_ERR_DEVICE_WAIT) and never as a hung GPU.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+__constant__ unsigned long long c_wait_limit_ns = kWaitLimitNs;
+
+__device__ __forceinline__ bool mbar_try_parity(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false = gave up after limit_ns
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_parity(bar, parity)) return true;
+        if (i < 64) continue;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > limit_ns) return false;
+        __nanosleep(32);
+    }
+}
+
 // ---- optional timeline stamps (debug builds with -DSLLM_TIMELINE only) ------------------------------------
 #ifdef SLLM_TIMELINE
 __device__ unsigned long long g_tl_buf[1 << 16];

@@ -16,6 +16,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <random>
 #include <string>
 #include <tuple>
@@ -146,6 +147,7 @@ struct sllm_engine {
     int iter_launches = 0;             // kernels in the decode-iteration graph captured last
     float last_step_ms = 0.f;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    std::vector<cudaEvent_t> step_events;      // sllm_decode_loop_timed
     size_t max_dyn_smem = 0;
 };
 
@@ -774,9 +776,18 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, int iters, cudaGrap
 
 int launches_per_iteration(const sllm_engine* e) { return e->iter_launches; }
 
+int status_error(sllm_engine* e, unsigned int st) {
+    cudaMemsetAsync(e->d_status, 0, sizeof st, e->stream);
+    return fail(e, SLLM_ERR_DEVICE_WAIT, "a bounded device-side wait gave up (code " + std::to_string(st) + ")");
+}
+
+// Finished flags of the live slots plus the device status word, in one synchronisation.
 int check_finished_flags(sllm_engine* e, bool* all_done, bool* nonfinite) {
+    int* h_status = e->h_flags + e->max_batch;
     CU(cudaMemcpyAsync(e->h_flags, e->st.finished, e->n_live * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaMemcpyAsync(h_status, e->d_status, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     CU(cudaStreamSynchronize(e->stream));
+    if (*h_status) return status_error(e, (unsigned int)*h_status);
     *all_done = true; *nonfinite = false;
     for (int s = 0; s < e->n_live; ++s) {
         if (e->h_flags[s] == 0) *all_done = false;
@@ -785,19 +796,13 @@ int check_finished_flags(sllm_engine* e, bool* all_done, bool* nonfinite) {
     return SLLM_OK;
 }
 
+// The draw buffer is allocated once at creation (max_batch x token capacity of a slot): no call of the token loop
+// allocates, and the cached graphs keep a valid pointer for the engine's lifetime.
 int upload_draws(sllm_engine* e, const double* host, size_t n_slots, size_t stride, bool transpose_from_step_major) {
     const size_t n = n_slots * stride;
-    if (n > e->draws_cap) {
-        if (e->d_draws) {
-            CU(cudaStreamSynchronize(e->stream));
-            cudaFree(e->d_draws);
-            for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);   // they hold the old pointer
-            e->graphs.clear();
-        }
-        e->d_draws = nullptr;
-        CU(cudaMalloc((void**)&e->d_draws, n * sizeof(double)));
-        e->draws_cap = n;
-    }
+    if (n > e->draws_cap)
+        return fail(e, SLLM_ERR_CAPACITY, "more draws than the engine's draw buffer holds (max_batch x (2 * context_length + 2)): "
+                                          "ask for fewer steps per call");
     if (!transpose_from_step_major || n_slots == 1) {
         CU(cudaMemcpyAsync(e->d_draws, host, n * sizeof(double), cudaMemcpyHostToDevice, e->stream));
         CU(cudaStreamSynchronize(e->stream));
@@ -964,10 +969,7 @@ int check_status(sllm_engine* e) {
     unsigned int st = 0;
     CU(cudaMemcpyAsync(&st, e->d_status, sizeof st, cudaMemcpyDeviceToHost, e->stream));
     CU(cudaStreamSynchronize(e->stream));
-    if (st) {
-        CU(cudaMemsetAsync(e->d_status, 0, sizeof st, e->stream));
-        return fail(e, SLLM_ERR_DEVICE_WAIT, "a bounded device-side wait gave up (code " + std::to_string(st) + ")");
-    }
+    if (st) return status_error(e, st);
     return SLLM_OK;
 }
 
@@ -1110,6 +1112,10 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     e->pages_per_seq = (m.ctx + kPage - 1) / kPage;
     e->n_pages = (opt.kv_pages ? (long long)opt.kv_pages : (long long)e->max_batch * e->pages_per_seq) + 1;   // + the spare page
     e->spare_page = (int)(e->n_pages - 1);
+    if (const char* v = std::getenv("SLLM_WAIT_LIMIT_MS")) {        // diagnostic: how long a device-side wait polls before it gives up
+        const unsigned long long ns = (unsigned long long)std::min(std::max(std::atoll(v), 1ll), 60000ll) * 1000000ull;
+        if (cudaMemcpyToSymbol(c_wait_limit_ns, &ns, sizeof ns) != cudaSuccess) { e->err = "cannot set the wait limit"; return bail(SLLM_ERR_CUDA); }
+    }
     if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
     if (const char* v = std::getenv("SLLM_TC_SPLIT")) e->tune_tc_split = std::max(0, std::atoi(v));
     if (const char* v = std::getenv("SLLM_STREAM_SPLITS")) e->tune_stream_splits = std::min(std::max(0, std::atoi(v)), 8);
@@ -1182,7 +1188,13 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             const size_t bytes = (size_t)L * e->n_pages * page_bytes;
             cudaError_t ce = cudaMalloc(&q, bytes);
             if (ce != cudaSuccess) { e->err = std::string("KV pool allocation failed: ") + cudaGetErrorString(ce); rc = SLLM_ERR_CUDA; }
-            else { e->allocs.push_back(q); e->kv_pool = q; e->kv_bytes = bytes; }
+            else {
+                e->allocs.push_back(q); e->kv_pool = q; e->kv_bytes = bytes;
+                // Kernels that multiply whole pages by zero probabilities (the tensor-core prefill attention) need
+                // finite values in rows no position has written yet: 0 x Inf/NaN would poison the product.  Pages
+                // that return to the pool hold finite K/V of their previous owner, so clearing once suffices.
+                cudaMemsetAsync(q, 0, bytes, e->stream);
+            }
         }
         (void)p;
         e->free_pages.resize(e->n_pages - 1);
@@ -1233,6 +1245,8 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->samp_pmax_val, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);
     A(&e->samp_pmax_idx, (size_t)e->max_batch * e->samp_bps_cap, &e->scratch_bytes);
     A(&e->d_status, 4, &e->scratch_bytes);
+    e->draws_cap = (size_t)e->max_batch * (size_t)e->st.tok_cap;
+    A(&e->d_draws, e->draws_cap, &e->scratch_bytes);
     if (!e->f32) {
         A(&e->xn16, (size_t)e->pass_cap * D, &e->scratch_bytes); A(&e->att16, (size_t)e->pass_cap * D, &e->scratch_bytes);
         e->ss_parts = 4 * (int)((D + kTcBM - 1) / kTcBM);
@@ -1272,7 +1286,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->part_o, (size_t)e->split_tok_cap * H * kMaxSplits * hd, &e->scratch_bytes);
     A(&e->part_ml, (size_t)e->split_tok_cap * H * kMaxSplits * 2, &e->scratch_bytes);
     A(&e->ticket, (size_t)e->split_tok_cap * H, &e->scratch_bytes);
-    if (!rc && cudaMallocHost((void**)&e->h_flags, std::max(e->max_batch, 16) * sizeof(int)) != cudaSuccess) {
+    if (!rc && cudaMallocHost((void**)&e->h_flags, (e->max_batch + 16) * sizeof(int)) != cudaSuccess) {
         e->err = "cudaMallocHost failed"; rc = SLLM_ERR_CUDA;
     }
     if (!rc && cudaStreamSynchronize(e->stream) != cudaSuccess) { e->err = "initialisation failed"; rc = SLLM_ERR_CUDA; }
@@ -1287,8 +1301,8 @@ void sllm_engine_destroy(sllm_engine* e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);
     for (void* p : e->allocs) cudaFree(p);
-    if (e->d_draws) cudaFree(e->d_draws);
     if (e->h_flags) cudaFreeHost(e->h_flags);
+    for (cudaEvent_t ev : e->step_events) cudaEventDestroy(ev);
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -1451,7 +1465,7 @@ int sllm_decode_step(sllm_engine* e) {
     CU(cudaStreamSynchronize(e->stream));
     cudaEventElapsedTime(&e->last_step_ms, e->ev0, e->ev1);
     e->decode_steps += 1;
-    return SLLM_OK;
+    return check_status(e);
 }
 
 int sllm_get_step_logits(sllm_engine* e, uint32_t slot, float* host) {
@@ -1619,8 +1633,13 @@ int sllm_slot_append(sllm_engine* e, uint32_t slot, const uint32_t* ids, uint32_
 int sllm_slot_release(sllm_engine* e, uint32_t slot) {
     if (!e || slot >= (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_slot_release: bad slot");
     if ((int)slot >= e->n_live) return SLLM_OK;
-    return park_slot(e, (int)slot);
+    int rc = park_slot(e, (int)slot);
+    // the live range ends at the highest slot that holds a sequence
+    while (e->n_live > 0 && e->slot_released[e->n_live - 1]) e->n_live -= 1;
+    return rc;
 }
+
+uint32_t sllm_num_live(const sllm_engine* e) { return e ? (uint32_t)e->n_live : 0; }
 
 int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n) {
     if (!e || !flags || n > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_get_finished: bad argument");
@@ -1706,11 +1725,17 @@ int sllm_decode_loop(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt,
     return decode_loop_impl(e, n_steps, opt, dd, (int)n_steps, 0, true, nullptr);
 }
 
-int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, uint64_t max_new,
-                  const sllm_sampling* opt, const double* draws, uint32_t* out, uint64_t out_stride, uint64_t* out_lens) {
+static int generate_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, uint64_t max_new,
+                         const sllm_sampling* opt, const double* draws, uint32_t* out, uint64_t out_stride, uint64_t* out_lens) {
     if (!e || !ids || !lens || !out || !out_lens) return fail(e, SLLM_ERR_INVALID, "sllm_generate: null argument");
     int rc = sampling_check(e, opt);
     if (rc) return rc;
+    // A slot's token buffer holds 2 * context_length + 2 ids: a request that could outgrow it is refused here rather
+    // than cut short without notice (the reference slides its window without bound).
+    for (uint32_t s = 0; s < n_seq && s < (uint32_t)e->max_batch; ++s)
+        if ((uint64_t)lens[s] + max_new > (uint64_t)e->st.tok_cap)
+            return fail(e, SLLM_ERR_CAPACITY, "sllm_generate: prompt plus max_new_tokens exceed a slot's token buffer "
+                                              "(2 * context_length + 2)");
     rc = load_slots(e, ids, lens, n_seq, /*allow_long=*/true);
     if (rc) return rc;
     if (max_new > 0) {
@@ -1784,6 +1809,64 @@ int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uin
     return SLLM_OK;
 }
 
+// sllm_decode_loop with one CUDA event between consecutive iterations (each iteration is one graph replay):
+// step_ms[i] = device time of iteration i.  For latency percentiles; the untimed loop replays 8 iterations per graph.
+int sllm_decode_loop_timed(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* draws, float* step_ms) {
+    if (!e || !step_ms) return fail(e, SLLM_ERR_INVALID, "sllm_decode_loop_timed: null argument");
+    int rc = sampling_check(e, opt);
+    if (rc) return rc;
+    if (e->n_live == 0) return fail(e, SLLM_ERR_STATE, "sllm_decode_loop_timed: no live slots");
+    if (n_steps == 0) return SLLM_OK;
+    if (n_steps > 65536) return fail(e, SLLM_ERR_CAPACITY, "sllm_decode_loop_timed: at most 65536 steps per call");
+    const double* dd = nullptr;
+    if (opt->temperature > 0.0f) {
+        if (!draws) return fail(e, SLLM_ERR_INVALID, "sllm_decode_loop_timed: draws required when temperature > 0");
+        rc = upload_draws(e, draws, e->n_live, n_steps, true);
+        if (rc) return rc;
+        dd = e->d_draws;
+        CU(cudaMemsetAsync(e->st.draw_idx, 0, e->n_live * sizeof(int), e->stream));
+    }
+    const SampleArgs s = make_sample_args(e, opt, e->n_live, dd, (int)n_steps, 0);
+    rc = refresh_attn_order(e);
+    if (rc) return rc;
+    cudaGraphExec_t ge = nullptr;
+    int per_iter = 0;
+    if (e->opt.use_graph) {
+        rc = get_iteration_graph(e, s, 1, &ge);
+        if (rc) return rc;
+        per_iter = launches_per_iteration(e);
+    }
+    while (e->step_events.size() < n_steps + 1) {
+        cudaEvent_t ev = nullptr;
+        CU(cudaEventCreate(&ev));
+        e->step_events.push_back(ev);
+    }
+    for (uint64_t i = 0; i < n_steps; ++i) {
+        rc = grow_for_step(e);
+        if (rc) return rc;
+        CU(cudaEventRecord(e->step_events[i], e->stream));
+        if (ge) { CU(cudaGraphLaunch(ge, e->stream)); e->launches += per_iter; }
+        else { rc = enqueue_iteration(e, s); if (rc) return rc; }
+        e->decode_steps += 1;
+    }
+    CU(cudaEventRecord(e->step_events[n_steps], e->stream));
+    bool all_done, nonfinite;
+    rc = check_finished_flags(e, &all_done, &nonfinite);
+    if (rc) return rc;
+    if (nonfinite) return fail(e, SLLM_ERR_NONFINITE, "Inference::generate: all logits are non-finite");
+    for (uint64_t i = 0; i < n_steps; ++i) CU(cudaEventElapsedTime(&step_ms[i], e->step_events[i], e->step_events[i + 1]));
+    return SLLM_OK;
+}
+
+int sllm_generate(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint32_t n_seq, uint64_t max_new,
+                  const sllm_sampling* opt, const double* draws, uint32_t* out, uint64_t out_stride, uint64_t* out_lens) {
+    try {
+        return generate_impl(e, ids, lens, n_seq, max_new, opt, draws, out, out_stride, out_lens);
+    } catch (const std::exception& ex) {            // host allocation failure: nothing may unwind through the C ABI
+        return fail(e, SLLM_ERR_CAPACITY, std::string("sllm_generate: ") + ex.what());
+    }
+}
+
 // ---- single-kernel entry points ------------------------------------------------------------------------------
 namespace {
 
@@ -1797,6 +1880,7 @@ static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticTick
 
 // device address of the array per device ordinal, looked up once with that device current
 unsigned char* g_static_scratch_addr[64] = {};
+std::mutex g_static_scratch_mutex;
 
 int attn_decode_launch(sllm_engine* e, uint32_t layer, uint32_t n_tok, const float* d_q, const int32_t* d_slot,
                        const int32_t* d_pos, uint32_t n_splits, float* d_out, cudaStream_t stream, float* part_o,
@@ -1870,6 +1954,7 @@ int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, co
     CU(cudaGetDevice(&cur));
     if (cur != e->dev || cur < 0 || cur >= 64)
         return fail(e, SLLM_ERR_STATE, "sllm_k_attn_decode_static: the engine's device must be the current device");
+    std::lock_guard<std::mutex> guard(g_static_scratch_mutex);      // the table is shared by every engine of the process
     if (!g_static_scratch_addr[cur]) {
         // The array's name is only a host-side handle: the kernel needs the address the symbol has on
         // THIS device, which the runtime reports once the device is current.
@@ -1886,6 +1971,87 @@ int sllm_k_attn_decode_static(sllm_engine* e, uint32_t layer, uint32_t n_tok, co
                               reinterpret_cast<float*>(base + kStaticTicketBytes + kStaticMlBytes),
                               reinterpret_cast<float*>(base + kStaticTicketBytes),
                               reinterpret_cast<unsigned int*>(base));
+}
+
+extern "C++" {
+namespace {
+// K/V rows of one slot between the host ([n_pos][num_heads * head_dim] fp32) and the paged cache (cache element type).
+template <typename KVT, bool WRITE>
+__global__ void __launch_bounds__(256) k_kv_rows(KvView kv, ModelDims m, int layer, int slot, int pos0, float* k_rows, float* v_rows) {
+    const int p = pos0 + blockIdx.x;
+    const int page = kv.block_table[(size_t)slot * kv.pages_per_seq + p / kPage];
+    for (int c = threadIdx.x; c < m.D; c += blockDim.x) {
+        const int h = c / m.hd, d = c % m.hd;
+        KVT* kp = kv_ptr<KVT>(kv, m, layer, page, 0, h, p % kPage) + d;
+        KVT* vp = kv_ptr<KVT>(kv, m, layer, page, 1, h, p % kPage) + d;
+        const size_t i = (size_t)blockIdx.x * m.D + c;
+        if (WRITE) { *kp = from_float<KVT>(k_rows[i]); *vp = from_float<KVT>(v_rows[i]); }
+        else { k_rows[i] = to_float(*kp); v_rows[i] = to_float(*vp); }
+    }
+}
+
+int kv_rows_impl(sllm_engine* e, uint32_t layer, uint32_t slot, uint32_t pos0, uint32_t n_pos, float* k, float* v, bool write) {
+    if (!e || !k || !v) return fail(e, SLLM_ERR_INVALID, "sllm_kv_rows: null argument");
+    const ModelDims& m = e->md;
+    if (layer >= (uint32_t)m.L) return fail(e, SLLM_ERR_INVALID, "sllm_kv_rows: layer out of range");
+    if (slot >= (uint32_t)e->n_live || e->slot_released[slot]) return fail(e, SLLM_ERR_STATE, "sllm_kv_rows: slot holds no sequence");
+    if (n_pos == 0) return SLLM_OK;
+    if ((uint64_t)pos0 + n_pos > (uint64_t)e->slot_pages[slot].size() * kPage)
+        return fail(e, SLLM_ERR_INVALID, "sllm_kv_rows: positions beyond the pages the slot holds");
+    const KvView kv{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    // staged through the pass buffers q (K rows) and att (V rows), a pass's worth of positions at a time
+    for (uint32_t b = 0; b < n_pos; b += (uint32_t)e->pass_cap) {
+        const uint32_t n = std::min<uint32_t>((uint32_t)e->pass_cap, n_pos - b);
+        const size_t bytes = (size_t)n * m.D * sizeof(float), off = (size_t)b * m.D;
+        if (write) {
+            CU(cudaMemcpyAsync(e->q, k + off, bytes, cudaMemcpyHostToDevice, e->stream));
+            CU(cudaMemcpyAsync(e->att, v + off, bytes, cudaMemcpyHostToDevice, e->stream));
+        }
+        const int p0 = (int)(pos0 + b);
+        if (e->f32) {
+            if (write) k_kv_rows<float, true><<<n, 256, 0, e->stream>>>(kv, m, (int)layer, (int)slot, p0, e->q, e->att);
+            else k_kv_rows<float, false><<<n, 256, 0, e->stream>>>(kv, m, (int)layer, (int)slot, p0, e->q, e->att);
+        } else {
+            if (write) k_kv_rows<__nv_bfloat16, true><<<n, 256, 0, e->stream>>>(kv, m, (int)layer, (int)slot, p0, e->q, e->att);
+            else k_kv_rows<__nv_bfloat16, false><<<n, 256, 0, e->stream>>>(kv, m, (int)layer, (int)slot, p0, e->q, e->att);
+        }
+        CU(cudaGetLastError());
+        e->launches += 1;
+        if (!write) {
+            CU(cudaMemcpyAsync(k + off, e->q, bytes, cudaMemcpyDeviceToHost, e->stream));
+            CU(cudaMemcpyAsync(v + off, e->att, bytes, cudaMemcpyDeviceToHost, e->stream));
+        }
+        CU(cudaStreamSynchronize(e->stream));
+    }
+    return SLLM_OK;
+}
+
+// A block whose only thread waits on an mbarrier that nothing ever arrives at: the wait runs out after limit_ns, the
+// block raises the status word and returns.
+__global__ void k_wait_probe(unsigned long long limit_ns, unsigned int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(&bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait_bounded(b, 0, limit_ns)) atomicExch(status, 90u);
+}
+}  // namespace
+}  // extern "C++"
+
+int sllm_kv_write(sllm_engine* e, uint32_t layer, uint32_t slot, uint32_t pos0, uint32_t n_pos, const float* k_rows, const float* v_rows) {
+    return kv_rows_impl(e, layer, slot, pos0, n_pos, const_cast<float*>(k_rows), const_cast<float*>(v_rows), true);
+}
+int sllm_kv_read(sllm_engine* e, uint32_t layer, uint32_t slot, uint32_t pos0, uint32_t n_pos, float* k_rows, float* v_rows) {
+    return kv_rows_impl(e, layer, slot, pos0, n_pos, k_rows, v_rows, false);
+}
+
+int sllm_k_wait_probe(sllm_engine* e, uint32_t limit_us) {
+    if (!e) return SLLM_ERR_INVALID;
+    if (limit_us == 0 || limit_us > 100000) return fail(e, SLLM_ERR_INVALID, "sllm_k_wait_probe: limit must be 1..100000 microseconds");
+    k_wait_probe<<<1, 1, 0, e->stream>>>((unsigned long long)limit_us * 1000ull, e->d_status);
+    CU(cudaGetLastError());
+    e->launches += 1;
+    return check_status(e);
 }
 
 #ifdef SLLM_TIMELINE

@@ -28,7 +28,6 @@ template <int BN> __host__ __device__ constexpr int tc_epi_warps() { return BN >
 template <int BN> __host__ __device__ constexpr int tc_threads() { return 64 + 32 * tc_epi_warps<BN>(); }
 constexpr int kTcMaxStages = 16;
 constexpr int kTcMaxSplit = 8;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // a wait gives up after two seconds
 
 struct TcArgs {
     int R, K, n_tok;
@@ -82,24 +81,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) { return mbar_try_parity(bar, parity); }
 // bounded wait; false = gave up (status word raised)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int code) {
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (i < 64) continue;
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitLimitNs) break;
-        __nanosleep(32);
-    }
+    if (mbar_wait_bounded(bar, parity, c_wait_limit_ns)) return true;
     atomicExch(status, code);
     return false;
 }

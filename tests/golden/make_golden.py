@@ -77,10 +77,38 @@ def cross_entropy_vectors():
                         loss_masked=np.float32(r.cross_entropy(logits, masked, nv)))
 
 
+def model_init():
+    """The reference's own initial weights: Tensor::seed(7), then Model::Model (embedding, then per block q k v out
+    gate up down, out/down with std 0.02/sqrt(2L); src/model.cpp:15-29, src/nn/attention.cpp:39-45,
+    src/nn/swiglu.cpp:17-22)."""
+    r = RefModel(SMALL, ctor_seed=7)
+    ps = r.params()
+    np.savez_compressed(os.path.join(OUT, "model_init_ref.npz"), names=np.array([n for n, _ in ps]),
+                        sha=np.array([sha(a) for _, a in ps]), head=np.stack([a.reshape(-1)[:4] for _, a in ps]),
+                        std=np.array([float(a.std()) for _, a in ps]))
+
+
+def attention_op():
+    """ops::attention (src/ops/attention.cpp:143-184) on random q, k, v: [1, 2 heads, 200 positions, 32]."""
+    import ctypes as C
+    r = RefModel(SMALL)
+    rng = np.random.default_rng(11)
+    H, T, hd = 2, 200, 32
+    q, k, v = (rng.normal(0, 1.0, (1, H, T, hd)).astype(np.float32) for _ in range(3))
+    out = np.empty_like(q)
+    f32p = C.POINTER(C.c_float)
+    rc = r.lib.ref_op_attention(q.ctypes.data_as(f32p), k.ctypes.data_as(f32p), v.ctypes.data_as(f32p), 1, H, T, hd,
+                                out.ctypes.data_as(f32p))
+    assert rc == 0
+    np.savez_compressed(os.path.join(OUT, "attention_op_ref.npz"), q=q, k=k, v=v, out=out)
+
+
 if __name__ == "__main__":
     if build_ref() is None:
         sys.exit("reference tree not available; golden vectors can only be regenerated where it is")
     small()
     c1_probe()
     cross_entropy_vectors()
+    model_init()
+    attention_op()
     print("golden vectors written to", OUT)

@@ -20,3 +20,28 @@ def test_cpp_facade_compiles_and_fails_loudly_without_gpu(tmp_path):
     r = subprocess.run([exe], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "no CUDA device" in r.stdout
+
+
+def test_model_constructor_initialises_like_the_reference(tmp_path, golden_dir):
+    """Model(config) after Tensor::seed(7): every parameter bit-equal with the reference constructor's (golden
+    hashes written by tests/golden/make_golden.py from the unmodified reference: embedding first, then per block
+    q k v out gate up down, out / down with std 0.02 / sqrt(2 L), gains 1)."""
+    import hashlib
+    import numpy as np
+    libdir = os.path.dirname(sl.lib_path())
+    exe, out = str(tmp_path / "facade_init"), str(tmp_path / "w.bin")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "facade_init.cpp"),
+                    "-o", exe, "-L", libdir, "-lsllm_b200", f"-Wl,-rpath,{libdir}"], check=True)
+    subprocess.run([exe, out, "7"], check=True)
+    g = np.load(os.path.join(golden_dir, "model_init_ref.npz"))
+    with open(out, "rb") as f:
+        n = int(np.frombuffer(f.read(4), np.uint32)[0])
+        assert n == len(g["names"]) == 20
+        for i in range(n):
+            nl = int(np.frombuffer(f.read(4), np.uint32)[0])
+            name = f.read(nl).decode()
+            ne = int(np.frombuffer(f.read(8), np.uint64)[0])
+            data = np.frombuffer(f.read(4 * ne), np.float32)
+            assert name == str(g["names"][i])
+            assert np.array_equal(data[:4], g["head"][i]), name
+            assert hashlib.sha256(data.tobytes()).hexdigest() == str(g["sha"][i]), name

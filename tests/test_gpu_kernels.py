@@ -128,3 +128,50 @@ def test_tensor_core_prefill_attention_full_context():
     # the last token is the arg-max of the oracle's logits for that window unless the top two are within the tolerance
     top2 = np.sort(want)[-2:]
     assert out[-1] == int(np.argmax(want)) or (top2[1] - top2[0]) <= 2e-2 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("fp32", [True, False])
+def test_attention_kernels_match_reference_op(fp32, golden_dir):
+    """The decode attention kernels against the reference's own ops::attention (src/ops/attention.cpp:143-184): q, k, v
+    and the expected output come from tests/golden/attention_op_ref.npz, written by the unmodified reference
+    (1 x 2 heads x 200 positions x 32).  K and V go into a slot's cache through sllm_kv_write; query t attends keys
+    0..t.  All three launch shapes are checked: the page-streaming kernel (200 tokens in one call), the split-K
+    flash-decode kernel (chunks of 50 tokens, 1 and 4 splits) and its allocation-free variant.  fp32 cache: only the
+    summation order differs (1e-5); bf16 cache: K and V are rounded to bf16 (2e-2)."""
+    import os
+    import torch
+    g = np.load(os.path.join(golden_dir, "attention_op_ref.npz"))
+    q, k, v, want = g["q"][0], g["k"][0], g["v"][0], g["out"][0]              # [H, T, hd]
+    H, T, hd = q.shape
+    cfg = Config(vocab=256, context=256, layers=1, d_model=H * hd, heads=H, ffn=64)
+    o, eng = make_pair(cfg, seed=1, stddev=0.05, fp32=fp32, via_checkpoint=False)
+    eng.prefill([prompt_ids(1, T, cfg.vocab)])                                  # the slot now holds pages for T positions
+    rows = lambda a: np.ascontiguousarray(a.transpose(1, 0, 2).reshape(T, H * hd))      # [T][H * hd]
+    eng.kv_write(0, 0, 0, rows(k), rows(v))
+    k_back, v_back = eng.kv_read(0, 0, 0, T)
+    if fp32:
+        assert np.array_equal(k_back, rows(k)) and np.array_equal(v_back, rows(v))
+    else:
+        assert np.abs(k_back - rows(k)).max() <= 2 ** -8 * np.abs(k).max()
+    qd = torch.from_numpy(rows(q)).cuda()
+    slot = torch.zeros(T, dtype=torch.int32, device="cuda")
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    expect = rows(want)
+    tol = 1e-5 if fp32 else 2e-2
+
+    def check(out, what):
+        torch.cuda.synchronize()
+        a = out.cpu().numpy()
+        assert np.isfinite(a).all(), what
+        assert np.abs(a - expect).max() <= tol * np.abs(expect).max(), (what, float(np.abs(a - expect).max()))
+
+    out = torch.full((T, H * hd), float("nan"), device="cuda")
+    eng.k_attn_decode(0, T, qd.data_ptr(), slot.data_ptr(), pos.data_ptr(), 1, out.data_ptr())
+    check(out, "streaming kernel")
+    for splits, static in ((1, False), (4, False), (4, True)):
+        out = torch.full((T, H * hd), float("nan"), device="cuda")
+        step = 50 if not static else 25                                          # 25 tokens x 2 heads fit the fixed scratch
+        for b in range(0, T, step):
+            eng.k_attn_decode(0, step, qd[b:].data_ptr(), slot[b:].data_ptr(), pos[b:].data_ptr(), splits, out[b:].data_ptr(),
+                              static_scratch=static)
+        check(out, f"flash-decode kernel, {splits} splits, static={static}")

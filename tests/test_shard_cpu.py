@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch.multiprocessing as mp
 
-from small_llm_b200.shard import shard_range
+from small_llm_b200.shard import balanced_assignment, shard_range
 
 
 def test_shard_range_covers_everything_once():
@@ -21,18 +21,34 @@ def test_shard_range_covers_everything_once():
         shard_range(4, 2, 2)
 
 
+def test_balanced_assignment_evens_out_total_length():
+    rng = np.random.default_rng(4)
+    lens = rng.integers(256, 1537, size=512)
+    for world in (1, 2, 4, 8):
+        parts = balanced_assignment(lens, world)
+        assert sorted(np.concatenate(parts).tolist()) == list(range(512))
+        assert {len(p) for p in parts} == {512 // world}
+        sums = [int(lens[p].sum()) for p in parts]
+        assert max(sums) - min(sums) <= 1536                       # within one sequence of each other
+    assert [p.tolist() for p in balanced_assignment([5, 9, 1], 2)] == [[1], [0, 2]]
+
+
 def _stream(i):                       # deterministic fake "generation" of sequence i
     return (np.arange(3 + i % 5, dtype=np.uint32) * 7 + i) % 32768
 
 
-def _worker(rank, world, port, n_seq, q):
+def _worker(rank, world, port, n_seq, q, balanced=False):
     import torch.distributed as dist
-    from small_llm_b200.shard import gather_streams, shard_range
+    from small_llm_b200.shard import balanced_assignment, gather_streams, shard_range
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    b, e = shard_range(n_seq, world, rank)
-    got = gather_streams([_stream(i) for i in range(b, e)], n_seq, 16)
+    if balanced:
+        parts = balanced_assignment([len(_stream(i)) for i in range(n_seq)], world)
+        got = gather_streams([_stream(int(i)) for i in parts[rank]], n_seq, 16, assignment=parts)
+    else:
+        b, e = shard_range(n_seq, world, rank)
+        got = gather_streams([_stream(i) for i in range(b, e)], n_seq, 16)
     if rank == 0:
         q.put([g.tolist() for g in got])
     else:
@@ -41,12 +57,12 @@ def _worker(rank, world, port, n_seq, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n_seq", [(2, 5), (3, 7), (2, 2)])
-def test_gather_streams_gloo(world, n_seq):
+@pytest.mark.parametrize("world,n_seq,balanced", [(2, 5, False), (3, 7, False), (2, 2, False), (2, 7, True)])
+def test_gather_streams_gloo(world, n_seq, balanced):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + world * 10 + n_seq
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n_seq, q)) for r in range(world)]
+    port = 29600 + world * 10 + n_seq + (100 if balanced else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_seq, q, balanced)) for r in range(world)]
     for p in procs:
         p.start()
     got = q.get(timeout=120)
