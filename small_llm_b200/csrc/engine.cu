@@ -29,6 +29,7 @@
 #include "attn_stream.cuh"
 #include "common.cuh"
 #include "decode_fused.cuh"
+#include "decode_persist.cuh"
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "repack.cuh"
@@ -127,6 +128,13 @@ struct sllm_engine {
     bool use_attn_stream = true;
     int fused_upc = 0, fused_nb = 0;
     bool fused_ok = false;
+    // persistent single-token decode kernel (decode_persist.cuh): bf16 weights, models whose per-block weight slices fit shared memory
+    bool persist_ok = false;
+    int ps_na = 0, ps_smax = 0, ps_ppsmax = 0;
+    size_t ps_smem = 0;
+    unsigned long long *ps_xa = nullptr, *ps_xb = nullptr, *ps_qkv = nullptr, *ps_ap = nullptr, *ps_hb = nullptr;
+    unsigned int* ps_epoch = nullptr;
+    LayerW* d_layers = nullptr;
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
@@ -584,7 +592,33 @@ int run_pass_fused_t(sllm_engine* e, const PassView& pv, int n_rows, float* logi
 
 int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl) { return launch_attn<__nv_bfloat16>(e, t, pdl); }
 
+template <int HD>
+int launch_persist_hd(sllm_engine* e, const PersistArgs& a, bool pdl) {
+    return launch(e, k_decode_persist<HD>, dim3(a.na), dim3(kPsThreads), e->ps_smem, pdl, a);
+}
+
+// One token through every layer and the head as a single resident kernel.
+int run_pass_persist(sllm_engine* e, const PassView& pv, int n_rows, float* logits, bool pdl) {
+    PersistArgs a{};
+    a.m = e->md; a.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
+    a.tok_id = pv.tok_id; a.tok_slot = pv.tok_slot; a.tok_pos = pv.tok_pos;
+    a.layers = e->d_layers; a.emb_f32 = e->emb_f32; a.emb_w = static_cast<const __nv_bfloat16*>(e->emb_w);
+    a.g_final = e->g_final; a.rope = e->rope;
+    a.xa = e->ps_xa; a.xb = e->ps_xb; a.qkv = e->ps_qkv; a.ap = e->ps_ap; a.hb = e->ps_hb;
+    a.epoch = e->ps_epoch; a.status = e->d_status;
+    a.logits = n_rows > 0 ? logits : nullptr; a.x_out = e->x;
+    a.na = e->ps_na; a.s_max = e->ps_smax; a.pps_max = e->ps_ppsmax;
+    switch (e->md.hd) {
+        case 16: return launch_persist_hd<16>(e, a, pdl);
+        case 32: return launch_persist_hd<32>(e, a, pdl);
+        case 64: return launch_persist_hd<64>(e, a, pdl);
+        case 128: return launch_persist_hd<128>(e, a, pdl);
+    }
+    return fail(e, SLLM_ERR_INVALID, "unsupported head_dim");
+}
+
 int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
+    if (pv.n_tok == 1 && e->persist_ok && (n_rows == 0 || row_tok == nullptr)) return run_pass_persist(e, pv, n_rows, logits, pdl);
     if (pv.n_tok == 1 && e->fused_ok && (n_rows == 0 || row_tok == nullptr))
         return e->f32 ? run_pass_fused_t<float>(e, pv, n_rows, logits, pdl) : run_pass_fused_t<__nv_bfloat16>(e, pv, n_rows, logits, pdl);
     if (!e->f32 && e->encode_tiled && pv.n_tok >= e->tc_min_tokens) return run_pass_tc(e, pv, row_tok, n_rows, logits, pdl);
@@ -1277,6 +1311,41 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
                 e->err = "cudaFuncSetAttribute failed for the prefill attention kernel"; rc = SLLM_ERR_CUDA;
             }
             if (!rc) { e->attn_tc = true; e->pf_tile_q = kPtQ; }
+        }
+        // persistent single-token decode: every block of the grid must own rows of every product, and its slices fit
+        if (!rc && std::getenv("SLLM_NO_PERSIST") == nullptr) {
+            int nc = e->sm_count;
+            if (const char* v = std::getenv("SLLM_PERSIST_CTAS")) nc = std::max(1, std::min(nc, std::atoi(v)));
+            const int na = (int)std::min<uint64_t>({(uint64_t)nc, D, F, 3 * D / 2});
+            if (na >= (int)H && L <= 120) {
+                const int s_max = na / (int)H;
+                const int pps_max = std::max(2, (e->pages_per_seq + s_max - 1) / s_max);
+                const PsLayout lay = ps_layout(m, na, s_max, pps_max, e->pages_per_seq);
+                if (lay.total <= e->max_dyn_smem && lay.head_stages >= 2) {
+                    e->ps_na = na; e->ps_smax = s_max; e->ps_ppsmax = pps_max; e->ps_smem = lay.total;
+                    A(&e->ps_xa, D, &e->scratch_bytes); A(&e->ps_xb, D, &e->scratch_bytes);
+                    A(&e->ps_qkv, 3 * D, &e->scratch_bytes);
+                    A(&e->ps_ap, (size_t)H * s_max * (hd + 2), &e->scratch_bytes);
+                    A(&e->ps_hb, F, &e->scratch_bytes);
+                    A(&e->ps_epoch, 4, &e->scratch_bytes);
+                    A(&e->d_layers, L, &e->scratch_bytes);
+                    if (!rc) {
+                        const unsigned int one = 1;
+                        cudaMemcpyAsync(e->ps_epoch, &one, sizeof one, cudaMemcpyHostToDevice, e->stream);
+                        cudaMemcpyAsync(e->d_layers, e->layers.data(), L * sizeof(LayerW), cudaMemcpyHostToDevice, e->stream);
+                        cudaStreamSynchronize(e->stream);
+                        cudaError_t ce = cudaSuccess;
+                        switch (hd) {
+                            case 16: ce = cudaFuncSetAttribute(k_decode_persist<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
+                            case 32: ce = cudaFuncSetAttribute(k_decode_persist<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
+                            case 64: ce = cudaFuncSetAttribute(k_decode_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
+                            default: ce = cudaFuncSetAttribute(k_decode_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
+                        }
+                        if (ce != cudaSuccess) { e->err = "cudaFuncSetAttribute failed for the persistent decode kernel"; rc = SLLM_ERR_CUDA; }
+                        else e->persist_ok = true;
+                    }
+                }
+            }
         }
         if (!rc) rc = configure_tc<kModeQKV>(e);
         if (!rc) rc = configure_tc<kModeResidual>(e);

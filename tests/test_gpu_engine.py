@@ -386,3 +386,47 @@ def test_sampler_with_one_block_per_slot_at_large_batch():
     for i in (0, 1, 17, 160, 299, 319):
         ref = o.generate(prompts[i], n_new, 0.9, 0.9, 1.1, us=us[:, i].astype(np.float32), eos=SMALL_EOS)
         assert np.array_equal(got[i], ref), i
+
+
+@pytest.mark.parametrize("cfg,std", [(MID, 0.05), (ODD, 0.05), (SMALL, 0.05), (FULL, 0.02)], ids=["hd32", "hd16", "small", "100m-hd64"])
+def test_persistent_decode_kernel_against_oracle_and_layerwise_kernels(cfg, std, monkeypatch):
+    """Batch-1 decode in bf16 runs as one resident kernel per token (every layer and the head; vectors handed between
+    blocks as tagged words).  Teacher-forced over a context that crosses page boundaries: its logits against the
+    oracle (2e-2) and against the two-kernels-per-layer path it replaces (same arithmetic, other summation order),
+    which SLLM_NO_PERSIST selects; then a free-running greedy generation must give the same stream on both paths
+    unless the oracle's top-2 margin is small."""
+    T = min(cfg.context, 200)
+    ids = prompt_ids(2, T, cfg.vocab)
+    o, eng = make_pair(cfg, seed=5, stddev=std, fp32=False, via_checkpoint=False)
+    monkeypatch.setenv("SLLM_NO_PERSIST", "1")
+    _, old = make_pair(cfg, seed=5, stddev=std, fp32=False, via_checkpoint=False)
+    monkeypatch.delenv("SLLM_NO_PERSIST")
+    ref = o.forward(ids, 1, T)[0]
+    n0 = 3
+    opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
+    worst_ref, worst_old = 0.0, 0.0
+    for e in (eng, old):
+        e.prefill([ids[:n0]])
+    for t in range(n0, T):
+        for e in (eng, old):
+            e.sample(opt, eos=cfg.vocab + 5)
+            e.force_token(0, int(ids[t]))
+            e.decode_step()
+        a, b = eng.step_logits(0), old.step_logits(0)
+        worst_ref = max(worst_ref, rel_err(a, ref[t]))
+        worst_old = max(worst_old, rel_err(a, b))
+    assert worst_ref <= TOL_BF16, worst_ref
+    assert worst_old <= 5e-3, worst_old
+    assert np.array_equal(eng.tokens(0), ids)
+    # one-token prompt: the kernel without its head (the prefill path asks for the residual only)
+    one = eng.forward_logits(ids[:1], 1, 1)
+    assert rel_err(one, o.forward(ids[:1], 1, 1)) <= TOL_BF16
+    # the graph-replayed loop
+    n_new = 40
+    got = eng.generate([ids[:20]], n_new, opt, eos=cfg.vocab + 5)[0]
+    want = old.generate([ids[:20]], n_new, opt, eos=cfg.vocab + 5)[0]
+    if not np.array_equal(got, want):
+        first = int(np.argmax(got != want))
+        rl = o.forward(got[:first], 1, first)[0, -1]
+        _, margin = greedy(rl, got[:first], 1.0)
+        assert margin < 1e-2, (first, margin)
