@@ -236,6 +236,7 @@ public:
         options_ = o;
         options_.weight_dtype = dt;
     }
+    const sllm_engine_options& engine_options() const { return options_; }
     // the C-ABI handle behind this model (built and loaded on first use)
     sllm_engine* engine() {
         if (!on_cuda_) throw std::logic_error("Model: this build has no CPU path; call to(Device::CUDA) first");

@@ -316,8 +316,10 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
     // the first layer's weights do not depend on the previous kernel: fetch them before the dependency wait
     issue_qkv(0); issue_o(0); issue_gu(0); issue_d(0);
     for (int k = tid; k < D; k += kPsThreads) s_gfinal[k] = a.g_final[k];
+    SLLM_TL(400);
     pdl_launch_dependents();
     pdl_wait();
+    SLLM_TL(401);
 
     bool live = *reinterpret_cast<volatile unsigned int*>(a.status) == 0u;     // an earlier failure: do nothing but drain
     const uint32_t epoch = *a.epoch;
@@ -362,8 +364,11 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             __syncthreads();
             if (*s_abort) { live = false; break; }
         }
+        SLLM_TL(410);
         if (!wait_bar(PS_B_QKV, 71u)) { live = false; break; }
+        SLLM_TL(411);
         ps_norm(xraw, s_gattn, xn, s_red, D, m.eps);
+        SLLM_TL(412);
         // ---- this block's QKV row pairs: RoPE, K/V to the cache, all three to the consumers -----------------------
         for (int pi = warp; pi < pp1 - pp0; pi += kPsWarps) {
             float r0, r1;
@@ -387,6 +392,7 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             if (lane == 0) { ll_st(a.qkv + row, o0, tg + 1u); ll_st(a.qkv + row + 1, o1, tg + 1u); }
         }
         __syncthreads();                                   // every warp is done with s_wqkv, s_gattn
+        SLLM_TL(413);
         if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_qkv(l + 1); }
         // ---- attention over this block's key range -------------------------------------------------------------------
         if (attn_cta) {
@@ -395,9 +401,11 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             ll_gather(a.qkv + (size_t)2 * D + (size_t)ah * HD, HD, tg + 1u, s_qh + 2 * HD, s_abort, a.status, 72u);
             __syncthreads();
             if (*s_abort) { live = false; break; }
+            SLLM_TL(414);
             float part = 0.f;                              // thread i < HD + 2: out[i] | max | sum of this key range
             if (my_pages > 0) {
                 if (!wait_bar(PS_B_KV, 73u)) { live = false; break; }
+                SLLM_TL(415);
                 const int kb = p_lo * kPage;
                 const int nk = min(my_pages * kPage, pos + 1 - kb);            // keys of this range that exist
                 const int sub = lane % LPK, rsub = lane / LPK;
@@ -452,12 +460,14 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             }
             if (tid < HD + 2) ll_st(a.ap + ((size_t)(ah * S + as) * (HD + 2) + tid), part, tg + 2u);
             __syncthreads();                               // s_kv is free: fetch the next layer's pages
+            SLLM_TL(416);
             if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_kv(l + 1); }
         }
         // ---- merge the key ranges of every head (in range order), out-projection rows, residual --------------------
         ll_gather(a.ap, H * S * (HD + 2), tg + 2u, s_ap, s_abort, a.status, 74u);
         __syncthreads();
         if (*s_abort) { live = false; break; }
+        SLLM_TL(417);
         for (int t = tid; t < D; t += kPsThreads) {
             const int h = t / HD, d = t - h * HD;
             const float* ph = s_ap + (size_t)h * S * (HD + 2);
@@ -474,18 +484,22 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             s_att[t] = num / den;
         }
         if (!wait_bar(PS_B_O, 75u)) { live = false; break; }      // its barrier also publishes s_att
+        SLLM_TL(418);
         for (int r = warp; r < nx; r += kPsWarps) {
             const float y = ps_dot(s_wo + (size_t)r * D, s_att, D);
             if (lane == 0) ll_st(a.xb + d0 + r, xraw[d0 + r] + y, tg + 3u);
         }
         __syncthreads();
+        SLLM_TL(419);
         if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_o(l + 1); }
         // ---- x after the attention half, norm, this block's hidden units ---------------------------------------------
         ll_gather(a.xb, D, tg + 3u, xraw, s_abort, a.status, 76u);
         __syncthreads();
         if (*s_abort) { live = false; break; }
+        SLLM_TL(420);
         if (!wait_bar(PS_B_GU, 77u)) { live = false; break; }
         ps_norm(xraw, s_gffn, xn, s_red, D, m.eps);
+        SLLM_TL(421);
         for (int u = warp; u < nu; u += kPsWarps) {
             float g, up;
             ps_dot2(s_wgu + (size_t)(2 * u) * D, s_wgu + (size_t)(2 * u + 1) * D, xn, D, g, up);
@@ -495,12 +509,15 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             }
         }
         __syncthreads();
+        SLLM_TL(422);
         if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_gu(l + 1); }
         // ---- all hidden units, down-projection rows, residual -----------------------------------------------------------
         ll_gather(a.hb, F, tg + 4u, s_hid, s_abort, a.status, 78u);
         __syncthreads();
         if (*s_abort) { live = false; break; }
+        SLLM_TL(423);
         if (!wait_bar(PS_B_D, 79u)) { live = false; break; }
+        SLLM_TL(424);
         for (int r = warp; r < nx; r += kPsWarps) {
             const float y = ps_dot(s_wd + (size_t)r * F, s_hid, F);
             if (lane == 0) {
@@ -510,6 +527,7 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             }
         }
         __syncthreads();
+        SLLM_TL(425);
         if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_d(l + 1); }
     }
 
@@ -532,6 +550,7 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
         ll_gather(a.xa, D, epoch * 1024u + (uint32_t)NL * 8u, xraw, s_abort, a.status, 80u);
         __syncthreads();
         bool go = *s_abort == 0;
+        SLLM_TL(430);
         if (go) ps_norm(xraw, s_gfinal, xn, s_red, D, m.eps);
         for (int st = 0; st < issued; ++st) {              // after a failure nothing more is issued: the loop drains
             const bool ok = mbar_wait_bounded(BAR(PS_B_HEAD + st % ns), (uint32_t)((st / ns) & 1), c_wait_limit_ns);
@@ -551,6 +570,7 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
         for (int b = 0; b < 5; ++b)
             while (n_waited[b] < n_issued[b]) { mbar_wait_bounded(BAR(b), (uint32_t)(n_waited[b] & 1), c_wait_limit_ns); n_waited[b] += 1; }
     }
+    SLLM_TL(432);
     if (cta == 0 && tid == 0) *a.epoch = epoch + 1u;
 }
 

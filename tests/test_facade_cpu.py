@@ -45,3 +45,21 @@ def test_model_constructor_initialises_like_the_reference(tmp_path, golden_dir):
             assert name == str(g["names"][i])
             assert np.array_equal(data[:4], g["head"][i]), name
             assert hashlib.sha256(data.tobytes()).hexdigest() == str(g["sha"][i]), name
+
+
+def test_cpp_balanced_assignment_matches_python(tmp_path):
+    """include/sllm_serving.hpp compiles on its own, and its balancedAssignment deals sequences exactly as the Python
+    host layer's (small_llm_b200.shard.balanced_assignment) does."""
+    import numpy as np
+    from small_llm_b200.shard import balanced_assignment
+    libdir = os.path.dirname(sl.lib_path())
+    exe = str(tmp_path / "serving_cpu")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-pthread", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "serving_cpu.cpp"), "-o", exe, "-L", libdir, "-lsllm_b200",
+                    f"-Wl,-rpath,{libdir}"], check=True)
+    rng = np.random.default_rng(3)
+    for world, n in ((1, 5), (2, 7), (3, 10), (8, 64)):
+        lens = rng.integers(1, 1537, size=n)
+        r = subprocess.run([exe, str(world)] + [str(int(x)) for x in lens], capture_output=True, text=True, check=True)
+        got = [[int(t) for t in line.split()] for line in r.stdout.strip("\n").split("\n")]
+        assert got == [p.tolist() for p in balanced_assignment(lens, world)]
