@@ -90,6 +90,10 @@ const char* sllm_last_error(const sllm_engine* e);
 int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* opt, sllm_engine** out);
 void sllm_engine_destroy(sllm_engine* e);
 int sllm_engine_stats(sllm_engine* e, sllm_stats* out);
+/* Makes the engine's GPU the calling thread's current CUDA device.  Every call on an engine must come from a thread
+ * whose current device is the engine's (sllm_engine_create leaves it so on the creating thread); a thread that takes
+ * an engine over, or drives engines of several GPUs, calls this first. */
+int sllm_engine_make_current(sllm_engine* e);
 /* cudaStream_t of the engine (as void*), for callers that time with events. */
 void* sllm_engine_stream(sllm_engine* e);
 

@@ -172,6 +172,7 @@ private:
             load_(*models_[r]);
         }
         sllm_engine* e = models_[r]->engine();
+        sllm_detail::check(sllm_engine_make_current(e), e);   // this thread is new: its current device is not yet the engine's
         sllm_sampling s;
         s.temperature = opt.temperature; s.top_p = opt.top_p; s.repetition_penalty = opt.repetition_penalty;
         s.eos_token = eos_token; s.stop_token = opt.stop_token; s.seed = opt.seed;

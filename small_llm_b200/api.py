@@ -71,6 +71,7 @@ ABI_SYMBOLS = [
     "sllm_set_step_logits", "sllm_force_token", "sllm_truncate", "sllm_generate", "sllm_decode_loop", "sllm_k_attn_decode", "sllm_k_attn_decode_static",
     "sllm_eval_loss", "sllm_slot_assign", "sllm_slot_append", "sllm_slot_release", "sllm_get_finished", "sllm_num_live",
     "sllm_k_wait_probe", "sllm_kv_write", "sllm_kv_read", "sllm_decode_loop_timed",
+    "sllm_engine_make_current",
 ]
 
 
@@ -120,6 +121,7 @@ def load_library(path: str | None = None):
     lib.sllm_slot_release.argtypes = [E, C.c_uint32]
     lib.sllm_get_finished.argtypes = [E, i32p, C.c_uint32]
     lib.sllm_k_wait_probe.argtypes = [E, C.c_uint32]
+    lib.sllm_engine_make_current.argtypes = [E]
     lib.sllm_decode_loop_timed.argtypes = [E, C.c_uint64, C.POINTER(_Sampling), f64p, f32p]
     lib.sllm_kv_write.argtypes = [E, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, f32p, f32p]
     lib.sllm_kv_read.argtypes = [E, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, f32p, f32p]

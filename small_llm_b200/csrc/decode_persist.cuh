@@ -21,6 +21,10 @@
 //   * Every poll is bounded: a block that waits longer than the engine's wait limit raises the status word,
 //     waits (bounded) for its own copies in flight and returns; the others run into the same limit.
 //
+// Measured and dropped: requesting every polled word three times 0.15 us apart (slower: 354 against 329 us per token
+// on the same GPU), splitting a down-projection row over several warps (two more block barriers cost more than the
+// shorter sums saved).
+//
 // Buffers are reused by every layer.  That is safe because the hand-offs of x and of the hidden units are
 // all-to-all: a block writes hand-off k+1 only after it has read all of hand-off k, i.e. after every block wrote k,
 // i.e. after every block finished reading everything before k.
@@ -33,10 +37,11 @@
 
 namespace sllm {
 
-constexpr int kPsThreads = 512;
+constexpr int kPsThreads = 512;         // threads that compute; one more warp only issues the bulk copies
 constexpr int kPsWarps = kPsThreads / 32;
-constexpr int kPsHeadRows = 16;          // vocabulary rows per head stage (one per warp)
-constexpr int kPsMaxHeadStages = 8;
+constexpr int kPsBlock = kPsThreads + 32;
+constexpr int kPsHeadRows = 32;          // vocabulary rows per head stage (two per warp)
+constexpr int kPsMaxHeadStages = 12;
 
 struct PersistArgs {
     ModelDims m;
@@ -61,19 +66,20 @@ struct PersistArgs {
     int na;                              // blocks of the grid (every one owns rows of every product)
     int s_max;                           // key ranges per head at most (na / H)
     int pps_max;                         // KV pages per key range at most
+    uint32_t smem_total;                 // dynamic shared memory of the launch
 };
 
 // ---- shared-memory layout, the same arithmetic on host and device ---------------------------------------------
 struct PsLayout {
     int rq, rx, ru;                      // most QKV rows, residual rows, hidden units of any block
     uint32_t o_wqkv, o_wo, o_wgu, o_wd, o_kv, o_region_end;      // [o_wqkv, o_region_end) is reused by the head stages
-    uint32_t o_gattn, o_gffn, o_gfinal, o_xraw, o_xn, o_att, o_hid, o_ap, o_sc, o_qh, o_redo, o_rope, o_pages, o_red, o_bars;
-    uint32_t total;
-    int head_stages;
+    uint32_t o_gattn, o_gffn, o_gfinal, o_xraw, o_xn, o_att, o_hid, o_ap, o_sc, o_qh, o_redo, o_rope, o_pages, o_red, o_bars, o_head_pre;
+    uint32_t total;                      // bytes the layers need; the head's early stages take what is left of smem_total
+    int head_stages, head_pre;
 };
 __host__ __device__ inline uint32_t ps_align(uint32_t v) { return (v + 127u) & ~127u; }
 __host__ __device__ inline int ps_ceil_div(int a, int b) { return (a + b - 1) / b; }
-__host__ __device__ inline PsLayout ps_layout(const ModelDims& m, int na, int s_max, int pps_max, int pages_per_seq) {
+__host__ __device__ inline PsLayout ps_layout(const ModelDims& m, int na, int s_max, int pps_max, int pages_per_seq, uint32_t smem_total) {
     PsLayout L;
     L.rq = 2 * ps_ceil_div(3 * m.D / 2, na);
     L.rx = ps_ceil_div(m.D, na);
@@ -93,19 +99,26 @@ __host__ __device__ inline PsLayout ps_layout(const ModelDims& m, int na, int s_
     L.o_att = o;    o = ps_align(o + (uint32_t)m.D * 4);
     L.o_hid = o;    o = ps_align(o + (uint32_t)m.F * 4);
     L.o_ap = o;     o = ps_align(o + (uint32_t)m.H * s_max * (m.hd + 2) * 4);
-    L.o_sc = o;     o = ps_align(o + (uint32_t)pps_max * kPage * 4);
+    L.o_sc = o;     o = ps_align(o + (uint32_t)(pps_max * kPage > m.H * s_max ? pps_max * kPage : m.H * s_max) * 4);   // scores of a key range; later one weight per (head, range)
     L.o_qh = o;     o = ps_align(o + (uint32_t)3 * m.hd * 4);
-    L.o_redo = o;   o = ps_align(o + (uint32_t)(kPsThreads / (m.hd / 2)) * (m.hd + 1) * 4);
+    L.o_redo = o;   o = ps_align(o + (uint32_t)kPsWarps * (m.hd + 2) * 4);
     L.o_rope = o;   o = ps_align(o + (uint32_t)(m.hd / 2) * 8);
     L.o_pages = o;  o = ps_align(o + (uint32_t)pages_per_seq * 4);
     L.o_red = o;    o = ps_align(o + 64 * 4);
-    L.o_bars = o;   o = ps_align(o + (5 + kPsMaxHeadStages) * 8);
+    L.o_bars = o;   o = ps_align(o + 2 * (5 + kPsMaxHeadStages) * 8);
+    L.o_head_pre = o;
     L.total = o;
     const uint32_t stage = (uint32_t)kPsHeadRows * m.D * 2;
     int hs = (int)((L.o_region_end - L.o_wqkv) / stage);
-    L.head_stages = hs > kPsMaxHeadStages ? kPsMaxHeadStages : hs;
+    L.head_stages = hs > kPsMaxHeadStages / 2 ? kPsMaxHeadStages / 2 : hs;
+    int pre = smem_total > o ? (int)((smem_total - o) / stage) : 0;
+    L.head_pre = pre > kPsMaxHeadStages - L.head_stages ? kPsMaxHeadStages - L.head_stages : pre;
     return L;
 }
+
+// barrier of the kPsThreads computing threads (the copy-issuing warp is not part of it)
+__device__ __forceinline__ void ps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kPsThreads) : "memory"); }
+__device__ __forceinline__ void ps_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
 // ---- tagged words through L2 -------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned long long ll_ld(const unsigned long long* p) {
@@ -125,15 +138,23 @@ __device__ __forceinline__ unsigned long long ps_now() {
 
 // Copies n tagged words into dst as floats, polling each until it carries `tag`.  No barrier inside: the caller
 // synchronises.  A wait that runs out raises *s_abort (shared memory) and the status word.
-__device__ __forceinline__ void ll_gather(const unsigned long long* buf, int n, uint32_t tag, float* dst, volatile int* s_abort,
-                                          unsigned int* status, unsigned int code) {
-    constexpr int IF = 4;                    // words in flight per thread
+// seg_len / seg_stride: the words are n / seg_len runs of seg_len consecutive words, seg_stride apart in buf
+// (one run: seg_len = n).  With `gain`, dst2[i] = value * gain[i] is stored too and the thread's sum of squares of
+// the values is returned (for the RMSNorm that follows: y = (x * r) * g is applied as r * (W . (x * g))).
+template <int IF>
+__device__ __forceinline__ float ll_gather(const unsigned long long* buf, int n, int seg_len, int seg_stride, uint32_t tag, float* dst,
+                                           const float* gain, float* dst2, volatile int* s_abort, unsigned int* status,
+                                           unsigned int code) {
+    float ss = 0.f;
     for (int base = threadIdx.x; base < n; base += kPsThreads * IF) {
         unsigned long long v[IF];
+        const unsigned long long* src[IF];
 #pragma unroll
         for (int j = 0; j < IF; ++j) {
             const int idx = base + j * kPsThreads;
-            v[j] = idx < n ? ll_ld(buf + idx) : ((unsigned long long)tag << 32);
+            const int seg = idx / seg_len;
+            src[j] = buf + (size_t)seg * seg_stride + (idx - seg * seg_len);
+            v[j] = idx < n ? ll_ld(src[j]) : ((unsigned long long)tag << 32);
         }
 #pragma unroll
         for (int j = 0; j < IF; ++j) {
@@ -148,39 +169,63 @@ __device__ __forceinline__ void ll_gather(const unsigned long long* buf, int n, 
                     if (t0 == 0) t0 = now;
                     else if (now - t0 > c_wait_limit_ns) { *s_abort = 1; atomicExch(status, code); break; }
                 }
-                v[j] = ll_ld(buf + idx);
+                v[j] = ll_ld(src[j]);
             }
-            dst[idx] = __uint_as_float((uint32_t)v[j]);
+            const float x = __uint_as_float((uint32_t)v[j]);
+            dst[idx] = x;
+            if (gain) { dst2[idx] = x * gain[idx]; ss += x * x; }
         }
     }
+    return ss;
+}
+
+// Block-wide 1 / sqrt(mean(x^2) + eps) from the threads' partial sums of squares; contains the block barrier that also
+// publishes what the threads wrote to shared memory before the call.
+__device__ __forceinline__ float ps_inv_rms(float ss, float* red, int D, float eps) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    ps_sync();
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPsWarps; ++w) s += red[w];
+    return rsqrtf(s / (float)D + eps);
 }
 
 // ---- shared-memory arithmetic -------------------------------------------------------------------------------------
 // dot products of one / two bf16 rows in shared memory with an fp32 vector in shared memory; every lane gets the sums
-__device__ __forceinline__ float ps_dot(const __nv_bfloat16* w, const float* x, int K) {
-    const int lane = threadIdx.x & 31;
-    float acc = 0.f;
-    for (int c = lane; c < K / 8; c += 32) {
+__device__ __forceinline__ float ps_dot_part(const __nv_bfloat16* w, const float* x, int c_begin, int c_end) {
+    float a0 = 0.f, a1 = 0.f;                // two chains: the sum's latency is what bounds these products
+    for (int c = c_begin + (threadIdx.x & 31); c < c_end; c += 32) {
         float f[8];
         unpack16<__nv_bfloat16>(*reinterpret_cast<const uint4*>(w + c * 8), f);
         const float4 x0 = *reinterpret_cast<const float4*>(x + c * 8), x1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-        acc += f[0] * x0.x + f[1] * x0.y + f[2] * x0.z + f[3] * x0.w + f[4] * x1.x + f[5] * x1.y + f[6] * x1.z + f[7] * x1.w;
+        a0 += f[0] * x0.x + f[1] * x0.y + f[2] * x0.z + f[3] * x0.w;
+        a1 += f[4] * x1.x + f[5] * x1.y + f[6] * x1.z + f[7] * x1.w;
     }
-    return warp_sum(acc);
+    return a0 + a1;
 }
+__device__ __forceinline__ float ps_dot(const __nv_bfloat16* w, const float* x, int K) { return warp_sum(ps_dot_part(w, x, 0, K / 8)); }
 __device__ __forceinline__ void ps_dot2(const __nv_bfloat16* w0, const __nv_bfloat16* w1, const float* x, int K, float& r0, float& r1) {
     const int lane = threadIdx.x & 31;
-    float a0 = 0.f, a1 = 0.f;
+    float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
     for (int c = lane; c < K / 8; c += 32) {
         float f[8], g[8];
         unpack16<__nv_bfloat16>(*reinterpret_cast<const uint4*>(w0 + c * 8), f);
         unpack16<__nv_bfloat16>(*reinterpret_cast<const uint4*>(w1 + c * 8), g);
         const float4 x0 = *reinterpret_cast<const float4*>(x + c * 8), x1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-        a0 += f[0] * x0.x + f[1] * x0.y + f[2] * x0.z + f[3] * x0.w + f[4] * x1.x + f[5] * x1.y + f[6] * x1.z + f[7] * x1.w;
-        a1 += g[0] * x0.x + g[1] * x0.y + g[2] * x0.z + g[3] * x0.w + g[4] * x1.x + g[5] * x1.y + g[6] * x1.z + g[7] * x1.w;
+        a0 += f[0] * x0.x + f[1] * x0.y + f[2] * x0.z + f[3] * x0.w;
+        a1 += f[4] * x1.x + f[5] * x1.y + f[6] * x1.z + f[7] * x1.w;
+        b0 += g[0] * x0.x + g[1] * x0.y + g[2] * x0.z + g[3] * x0.w;
+        b1 += g[4] * x1.x + g[5] * x1.y + g[6] * x1.z + g[7] * x1.w;
     }
-    r0 = warp_sum(a0);
-    r1 = warp_sum(a1);
+    a0 += a1; b0 += b1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {           // the two reductions interleaved
+        a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+        b0 += __shfl_xor_sync(0xffffffffu, b0, o);
+    }
+    r0 = a0; r1 = b0;
 }
 
 __device__ __forceinline__ uint32_t ps_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -200,36 +245,30 @@ __device__ __forceinline__ void ps_part(int n, int parts, int i, int& b, int& e)
     e = (int)((long long)n * (i + 1) / parts);
 }
 
-// RMSNorm of xraw into xn with `gain` (shared memory): y = (x * r) * g, r = 1 / sqrt(mean(x^2) + eps)
-__device__ __forceinline__ void ps_norm(const float* xraw, const float* gain, float* xn, float* red, int D, float eps) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float ss = 0.f;
-    for (int k = tid; k < D; k += kPsThreads) { const float v = xraw[k]; ss += v * v; }
-    ss = warp_sum(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < kPsWarps; ++w) s += red[w];
-    const float inv = 1.0f / sqrtf(s / (float)D + eps);
-    for (int k = tid; k < D; k += kPsThreads) xn[k] = xraw[k] * inv * gain[k];
-    __syncthreads();
-}
+// Timeline stamps of debug builds (-DSLLM_TIMELINE) without a round trip per stamp: block 0 reserves a run of entries
+// once, then every stamp is two plain stores.
+#ifdef SLLM_TIMELINE
+#define PS_TL_INIT(n) unsigned int ps_tl_i = 0, ps_tl_end = 0; \
+    if (blockIdx.x == 0 && threadIdx.x == 0) { ps_tl_i = atomicAdd(&g_tl_n, (unsigned int)(n)); ps_tl_end = ps_tl_i + (n); }
+#define PS_TL(id) do { if (ps_tl_i < ps_tl_end && ps_tl_end <= (1u << 15)) { unsigned long long t_; \
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_tl_buf[2 * ps_tl_i] = (id); g_tl_buf[2 * ps_tl_i + 1] = t_; ++ps_tl_i; } } while (0)
+#else
+#define PS_TL_INIT(n)
+#define PS_TL(id)
+#endif
 
-enum { PS_B_QKV = 0, PS_B_O = 1, PS_B_GU = 2, PS_B_D = 3, PS_B_KV = 4, PS_B_HEAD = 5 };
+enum { PS_B_QKV = 0, PS_B_O = 1, PS_B_GU = 2, PS_B_D = 3, PS_B_KV = 4, PS_B_HEAD = 5, PS_N_BARS = 5 + kPsMaxHeadStages };
 
 template <int HD>
-__global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistArgs a) {
+__global__ void __launch_bounds__(kPsBlock, 1) k_decode_persist(const PersistArgs a) {
     extern __shared__ __align__(128) unsigned char ps_smem_raw[];
     unsigned char* smem = ps_smem_raw;
     constexpr int LPK = HD / 8;                  // lanes per key row (16-byte pieces)
     constexpr int KPI = 32 / LPK;                // keys per warp instruction
-    constexpr int DP = HD / 2;                   // threads across a value row (two dims each)
-    constexpr int KG = kPsThreads / DP;          // key groups in the PV product
     const ModelDims& m = a.m;
     const int D = m.D, F = m.F, H = m.H, NL = m.L, V = m.V;
     const int cta = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const PsLayout lay = ps_layout(m, a.na, a.s_max, a.pps_max, a.kv.pages_per_seq);
+    const PsLayout lay = ps_layout(m, a.na, a.s_max, a.pps_max, a.kv.pages_per_seq, a.smem_total);
     __nv_bfloat16* s_wqkv = reinterpret_cast<__nv_bfloat16*>(smem + lay.o_wqkv);
     __nv_bfloat16* s_wo = reinterpret_cast<__nv_bfloat16*>(smem + lay.o_wo);
     __nv_bfloat16* s_wgu = reinterpret_cast<__nv_bfloat16*>(smem + lay.o_wgu);
@@ -239,19 +278,20 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
     float* s_gffn = reinterpret_cast<float*>(smem + lay.o_gffn);
     float* s_gfinal = reinterpret_cast<float*>(smem + lay.o_gfinal);
     float* xraw = reinterpret_cast<float*>(smem + lay.o_xraw);
-    float* xn = reinterpret_cast<float*>(smem + lay.o_xn);
+    float* xg = reinterpret_cast<float*>(smem + lay.o_xn);             // x * gain of the norm ahead (1/rms is applied to the products)
     float* s_att = reinterpret_cast<float*>(smem + lay.o_att);
     float* s_hid = reinterpret_cast<float*>(smem + lay.o_hid);
     float* s_ap = reinterpret_cast<float*>(smem + lay.o_ap);
     float* s_sc = reinterpret_cast<float*>(smem + lay.o_sc);
     float* s_qh = reinterpret_cast<float*>(smem + lay.o_qh);
-    float* s_redo = reinterpret_cast<float*>(smem + lay.o_redo);       // [KG][HD + 1]: partial outputs and sums of the key groups
+    float* s_redo = reinterpret_cast<float*>(smem + lay.o_redo);       // [warp][HD + 2]: partial attention results of the warps
     float2* s_rope = reinterpret_cast<float2*>(smem + lay.o_rope);
     int* s_pages = reinterpret_cast<int*>(smem + lay.o_pages);
     float* s_red = reinterpret_cast<float*>(smem + lay.o_red);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_red + 32);
     const uint32_t bar0 = ps_smem(smem + lay.o_bars);
-    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    auto FULL = [&](int i) { return bar0 + 8u * (uint32_t)i; };                   // "the copy has landed"
+    auto FREE = [&](int i) { return bar0 + 8u * (uint32_t)(PS_N_BARS + i); };     // "the buffer may be overwritten"
 
     // this block's rows of every product
     int pp0, pp1, d0, d1, u0, u1, v0, v1;
@@ -260,75 +300,158 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
     ps_part(F, a.na, cta, u0, u1);               // hidden units: gate / up row pairs
     ps_part(V, a.na, cta, v0, v1);               // vocabulary rows of the head
     const int nq = 2 * (pp1 - pp0), nx = d1 - d0, nu = u1 - u0;
+    // the head's stages: slot i < n_pre lives in shared memory that nothing else uses, the others reuse the layers'
+    // weight and KV buffers once the last layer is done
+    const uint32_t stage_bytes = (uint32_t)kPsHeadRows * D * 2;
+    const int n_head_rows = v1 - v0, n_st = a.logits ? ps_ceil_div(n_head_rows, kPsHeadRows) : 0;
+    const int n_pre = lay.head_pre, ns = lay.head_pre + lay.head_stages;
+    auto head_slot = [&](int slot) -> unsigned char* {
+        return slot < n_pre ? smem + lay.o_head_pre + (size_t)slot * stage_bytes : smem + lay.o_wqkv + (size_t)(slot - n_pre) * stage_bytes;
+    };
+    const size_t page_elems = (size_t)kPage * HD;
 
+    PS_TL_INIT(20 * NL + 8);
     if (tid == 0) {
-        for (int i = 0; i < 5 + kPsMaxHeadStages; ++i) ps_bar_init(BAR(i));
+        for (int i = 0; i < 2 * PS_N_BARS; ++i) ps_bar_init(bar0 + 8u * (uint32_t)i);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *s_abort = 0;
     }
     __syncthreads();
-    // loads issued / waited per barrier, identical in every thread (uniform control flow)
-    int n_issued[5] = {0, 0, 0, 0, 0}, n_waited[5] = {0, 0, 0, 0, 0};
-    auto issue_qkv = [&](int l) {
-        if (tid == 0) {
-            const uint32_t bytes = (uint32_t)nq * D * 2;
-            ps_expect(BAR(PS_B_QKV), bytes + (uint32_t)D * 4);
-            ps_bulk(ps_smem(s_wqkv), reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wqkv) + (size_t)2 * pp0 * D, bytes, BAR(PS_B_QKV));
-            ps_bulk(ps_smem(s_gattn), a.layers[l].g_attn, (uint32_t)D * 4, BAR(PS_B_QKV));
-        }
-        n_issued[PS_B_QKV] += 1;
-    };
-    auto issue_o = [&](int l) {
-        if (tid == 0) {
-            const uint32_t bytes = (uint32_t)nx * D * 2;
-            ps_expect(BAR(PS_B_O), bytes);
-            ps_bulk(ps_smem(s_wo), reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wo) + (size_t)d0 * D, bytes, BAR(PS_B_O));
-        }
-        n_issued[PS_B_O] += 1;
-    };
-    auto issue_gu = [&](int l) {
-        if (tid == 0) {
-            const uint32_t bytes = (uint32_t)2 * nu * D * 2;
-            ps_expect(BAR(PS_B_GU), bytes + (uint32_t)D * 4);
-            ps_bulk(ps_smem(s_wgu), reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wgu) + (size_t)2 * u0 * D, bytes, BAR(PS_B_GU));
-            ps_bulk(ps_smem(s_gffn), a.layers[l].g_ffn, (uint32_t)D * 4, BAR(PS_B_GU));
-        }
-        n_issued[PS_B_GU] += 1;
-    };
-    auto issue_d = [&](int l) {
-        if (tid == 0) {
-            const uint32_t bytes = (uint32_t)nx * F * 2;
-            ps_expect(BAR(PS_B_D), bytes);
-            ps_bulk(ps_smem(s_wd), reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wd) + (size_t)d0 * F, bytes, BAR(PS_B_D));
-        }
-        n_issued[PS_B_D] += 1;
-    };
-    // every thread waits for the copy (cheap once it has landed); the block barrier that follows makes the verdict
-    // uniform: false = a wait ran out somewhere in the block
-    auto wait_bar = [&](int b, unsigned int code) -> bool {
-        const bool ok = mbar_wait_bounded(BAR(b), (uint32_t)(n_waited[b] & 1), c_wait_limit_ns);
-        n_waited[b] += 1;
-        if (!ok) { *s_abort = 1; atomicExch(a.status, code); }
-        __syncthreads();
-        return *s_abort == 0;
-    };
 
-    // the first layer's weights do not depend on the previous kernel: fetch them before the dependency wait
-    issue_qkv(0); issue_o(0); issue_gu(0); issue_d(0);
+    // ============================================================================================================
+    // The copy warp: one thread issues every bulk copy of the block, a layer ahead of its use, so that the computing
+    // threads never spend their time on it.  It learns that a buffer may be refilled from the FREE barriers, on which
+    // a computing thread arrives after the block barrier that ends the buffer's last use.
+    // ============================================================================================================
+    if (warp == kPsWarps) {
+        if (lane != 0) return;
+        auto issue = [&](int b, void* dst, const void* src, uint32_t bytes, const void* src2, void* dst2, uint32_t bytes2) {
+            ps_expect(FULL(b), bytes + bytes2);
+            ps_bulk(ps_smem(dst), src, bytes, FULL(b));
+            if (bytes2) ps_bulk(ps_smem(dst2), src2, bytes2, FULL(b));
+        };
+        auto issue_qkv = [&](int l) {
+            issue(PS_B_QKV, s_wqkv, reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wqkv) + (size_t)2 * pp0 * D, (uint32_t)nq * D * 2,
+                  a.layers[l].g_attn, s_gattn, (uint32_t)D * 4);
+        };
+        auto issue_o = [&](int l) {
+            issue(PS_B_O, s_wo, reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wo) + (size_t)d0 * D, (uint32_t)nx * D * 2, nullptr, nullptr, 0u);
+        };
+        auto issue_gu = [&](int l) {
+            issue(PS_B_GU, s_wgu, reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wgu) + (size_t)2 * u0 * D, (uint32_t)2 * nu * D * 2,
+                  a.layers[l].g_ffn, s_gffn, (uint32_t)D * 4);
+        };
+        auto issue_d = [&](int l) {
+            issue(PS_B_D, s_wd, reinterpret_cast<const __nv_bfloat16*>(a.layers[l].wd) + (size_t)d0 * F, (uint32_t)nx * F * 2, nullptr, nullptr, 0u);
+        };
+        auto issue_head = [&](int st) {
+            const int rows = min(kPsHeadRows, n_head_rows - st * kPsHeadRows);
+            issue(PS_B_HEAD + st % ns, head_slot(st % ns), a.emb_w + (size_t)(v0 + st * kPsHeadRows) * D, (uint32_t)rows * D * 2, nullptr, nullptr, 0u);
+        };
+        // bounded wait that also gives up when the block has aborted; false = stop issuing
+        auto wait_free = [&](uint32_t bar, uint32_t parity) -> bool {
+            unsigned long long t0 = 0;
+            for (uint32_t i = 0;; ++i) {
+                if (mbar_try_parity(bar, parity)) return true;
+                if ((i & 63u) != 63u) continue;
+                if (*s_abort) return false;
+                const unsigned long long now = ps_now();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > c_wait_limit_ns) { *s_abort = 1; atomicExch(a.status, 82u); return false; }
+            }
+        };
+        int full_uses[5] = {1, 1, 1, 1, 0};
+        int head_issued = 0;
+        // weights do not depend on the previous kernel: the first layer's slices and the first head stages are
+        // requested before the dependency wait
+        issue_qkv(0); issue_o(0); issue_gu(0); issue_d(0);
+        for (; head_issued < min(n_pre, n_st); ++head_issued) issue_head(head_issued);
+        pdl_launch_dependents();
+        pdl_wait();
+        bool go = *reinterpret_cast<volatile unsigned int*>(a.status) == 0u;
+        const int pos = a.tok_pos[0], slot = a.tok_slot[0];
+        const int n_pages = pos / kPage + 1;
+        const int pps = max(2, ps_ceil_div(n_pages, a.s_max));
+        const int S = ps_ceil_div(n_pages, pps);
+        const bool attn_cta = cta < H * S;
+        const int ah = attn_cta ? cta / S : 0, as = attn_cta ? cta % S : 0;
+        const int p_lo = min(n_pages, as * pps), p_hi = attn_cta ? min(n_pages, p_lo + pps) : p_lo;
+        const int my_pages = p_hi - p_lo;
+        int pages[8];
+        for (int p = 0; p < my_pages && p < 8; ++p) pages[p] = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + p_lo + p];
+        auto issue_kv = [&](int l) {
+            ps_expect(FULL(PS_B_KV), (uint32_t)(my_pages * 2 * page_elems * 2));
+            for (int p = 0; p < my_pages; ++p) {
+                ps_bulk(ps_smem(s_kv + (size_t)(2 * p) * page_elems), kv_ptr<__nv_bfloat16>(a.kv, m, l, pages[p], 0, ah, 0),
+                        (uint32_t)(page_elems * 2), FULL(PS_B_KV));
+                ps_bulk(ps_smem(s_kv + (size_t)(2 * p + 1) * page_elems), kv_ptr<__nv_bfloat16>(a.kv, m, l, pages[p], 1, ah, 0),
+                        (uint32_t)(page_elems * 2), FULL(PS_B_KV));
+            }
+            full_uses[PS_B_KV] += 1;
+        };
+        if (go && my_pages > 0) issue_kv(0);
+        for (int l = 1; l < NL && go; ++l) {               // refills, in the order in which the layer before frees the buffers
+            const uint32_t par = (uint32_t)((l - 1) & 1);
+            go = wait_free(FREE(PS_B_QKV), par);
+            if (go) { issue_qkv(l); full_uses[PS_B_QKV] += 1; }
+            if (go && my_pages > 0) { go = wait_free(FREE(PS_B_KV), par); if (go) issue_kv(l); }
+            if (go) go = wait_free(FREE(PS_B_O), par);
+            if (go) { issue_o(l); full_uses[PS_B_O] += 1; }
+            if (go) go = wait_free(FREE(PS_B_GU), par);
+            if (go) { issue_gu(l); full_uses[PS_B_GU] += 1; }
+            if (go) go = wait_free(FREE(PS_B_D), par);
+            if (go) { issue_d(l); full_uses[PS_B_D] += 1; }
+        }
+        if (go && n_st > head_issued) {
+            // the rest of the head's stages go through the layers' buffers: all of them are free once the last layer is done
+            const uint32_t par = (uint32_t)((NL - 1) & 1);
+            go = wait_free(FREE(PS_B_QKV), par) && (my_pages == 0 || wait_free(FREE(PS_B_KV), par)) && wait_free(FREE(PS_B_O), par) &&
+                 wait_free(FREE(PS_B_GU), par) && wait_free(FREE(PS_B_D), par);
+            for (; go && head_issued < min(ns, n_st); ++head_issued) issue_head(head_issued);
+            for (; go && head_issued < n_st; ++head_issued) {
+                go = wait_free(FREE(PS_B_HEAD + head_issued % ns), (uint32_t)((head_issued / ns - 1) & 1));
+                if (go) issue_head(head_issued); else break;
+            }
+        }
+        // let every copy in flight land before the block's shared memory is given to another block
+        for (int b = 0; b < 5; ++b)
+            if (full_uses[b] > 0) mbar_wait_bounded(FULL(b), (uint32_t)((full_uses[b] - 1) & 1), c_wait_limit_ns);
+        for (int st = max(0, head_issued - ns); st < head_issued; ++st)
+            mbar_wait_bounded(FULL(PS_B_HEAD + st % ns), (uint32_t)((st / ns) & 1), c_wait_limit_ns);
+        return;
+    }
+
+    // ============================================================================================================
+    // The computing threads
+    // ============================================================================================================
+    int n_waited[5] = {0, 0, 0, 0, 0};
+    // Every thread waits for the copy itself (a single probe once it has landed, which is the usual case: the copies
+    // run a layer ahead).  A wait that runs out raises the abort flag; the block acts on it at its next barrier.
+    auto wait_full = [&](int b, unsigned int code) {
+        if (!mbar_wait_bounded(FULL(b), (uint32_t)(n_waited[b] & 1), c_wait_limit_ns)) { *s_abort = 1; atomicExch(a.status, code); }
+        n_waited[b] += 1;
+    };
+    auto release = [&](int b) { if (tid == 0) ps_arrive(FREE(b)); };         // call after the barrier that ends the buffer's use
+
     for (int k = tid; k < D; k += kPsThreads) s_gfinal[k] = a.g_final[k];
-    SLLM_TL(400);
+    PS_TL(400);
     pdl_launch_dependents();
     pdl_wait();
-    SLLM_TL(401);
+    PS_TL(401);
 
-    bool live = *reinterpret_cast<volatile unsigned int*>(a.status) == 0u;     // an earlier failure: do nothing but drain
+    bool live = *reinterpret_cast<volatile unsigned int*>(a.status) == 0u;     // an earlier failure: do nothing
     const uint32_t epoch = *a.epoch;
     const int pos = a.tok_pos[0], slot = a.tok_slot[0];
     const uint32_t tok = a.tok_id[0];
     const int n_pages = pos / kPage + 1;
     for (int i = tid; i < HD / 2; i += kPsThreads) s_rope[i] = a.rope[(size_t)pos * (HD / 2) + i];
-    for (int i = tid; i < n_pages; i += kPsThreads) s_pages[i] = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + i];
-    for (int k = tid; k < D; k += kPsThreads) xraw[k] = a.emb_f32[(size_t)tok * D + k];
+    if (tid == 0) s_pages[0] = a.kv.block_table[(size_t)slot * a.kv.pages_per_seq + pos / kPage];
+    wait_full(PS_B_QKV, 71u);                    // the first layer's QKV slice and gain
+    float ss = 0.f;                              // layer 0: the embedding row takes the place of the gathered x
+    for (int k = tid; k < D; k += kPsThreads) {
+        const float x = a.emb_f32[(size_t)tok * D + k];
+        xraw[k] = x; xg[k] = x * s_gattn[k]; ss += x * x;
+    }
     // attention role: head ah, key range as of S; ranges of pps consecutive pages
     const int pps = max(2, ps_ceil_div(n_pages, a.s_max));
     const int S = ps_ceil_div(n_pages, pps);
@@ -336,43 +459,24 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
     const int ah = attn_cta ? cta / S : 0, as = attn_cta ? cta % S : 0;
     const int p_lo = min(n_pages, as * pps), p_hi = attn_cta ? min(n_pages, p_lo + pps) : p_lo;
     const int my_pages = p_hi - p_lo;
-    const size_t page_elems = (size_t)kPage * HD;
-    __syncthreads();
-    auto issue_kv = [&](int l) {
-        if (my_pages > 0) {
-            if (tid == 0) {
-                ps_expect(BAR(PS_B_KV), (uint32_t)(my_pages * 2 * page_elems * 2));
-                for (int p = 0; p < my_pages; ++p) {
-                    const int page = s_pages[p_lo + p];
-                    ps_bulk(ps_smem(s_kv + (size_t)(2 * p) * page_elems), kv_ptr<__nv_bfloat16>(a.kv, m, l, page, 0, ah, 0),
-                            (uint32_t)(page_elems * 2), BAR(PS_B_KV));
-                    ps_bulk(ps_smem(s_kv + (size_t)(2 * p + 1) * page_elems), kv_ptr<__nv_bfloat16>(a.kv, m, l, page, 1, ah, 0),
-                            (uint32_t)(page_elems * 2), BAR(PS_B_KV));
-                }
-            }
-            n_issued[PS_B_KV] += 1;
-        }
-    };
-    if (live) issue_kv(0);
-    const int page_new = s_pages[pos / kPage];
+    float inv = ps_inv_rms(ss, s_red, D, m.eps);         // its barrier publishes s_pages, s_rope, xraw, xg
+    const int page_new = s_pages[0];
 
     for (int l = 0; l < NL && live; ++l) {
         const uint32_t tg = epoch * 1024u + (uint32_t)l * 8u;
-        // ---- x entering the layer (layer 0: the embedding row, already in xraw) ----------------------------------
+        // ---- x entering the layer (layer 0: done above), with the gain product and the sum of squares ------------
         if (l > 0) {
-            ll_gather(a.xa, D, tg + 0u, xraw, s_abort, a.status, 70u);
-            __syncthreads();
+            wait_full(PS_B_QKV, 71u);
+            ss = ll_gather<4>(a.xa, D, D, 0, tg + 0u, xraw, s_gattn, xg, s_abort, a.status, 70u);
+            inv = ps_inv_rms(ss, s_red, D, m.eps);
             if (*s_abort) { live = false; break; }
         }
-        SLLM_TL(410);
-        if (!wait_bar(PS_B_QKV, 71u)) { live = false; break; }
-        SLLM_TL(411);
-        ps_norm(xraw, s_gattn, xn, s_red, D, m.eps);
-        SLLM_TL(412);
+        PS_TL(412);
         // ---- this block's QKV row pairs: RoPE, K/V to the cache, all three to the consumers -----------------------
         for (int pi = warp; pi < pp1 - pp0; pi += kPsWarps) {
             float r0, r1;
-            ps_dot2(s_wqkv + (size_t)(2 * pi) * D, s_wqkv + (size_t)(2 * pi + 1) * D, xn, D, r0, r1);
+            ps_dot2(s_wqkv + (size_t)(2 * pi) * D, s_wqkv + (size_t)(2 * pi + 1) * D, xg, D, r0, r1);
+            r0 *= inv; r1 *= inv;
             const int row = 2 * (pp0 + pi);
             const int which = row / D, col = row - which * D, head = col / HD, d = col - head * HD;
             float o0 = r0, o1 = r1;
@@ -391,133 +495,181 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
             }
             if (lane == 0) { ll_st(a.qkv + row, o0, tg + 1u); ll_st(a.qkv + row + 1, o1, tg + 1u); }
         }
-        __syncthreads();                                   // every warp is done with s_wqkv, s_gattn
-        SLLM_TL(413);
-        if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_qkv(l + 1); }
+        ps_sync();                                         // every warp is done with s_wqkv, s_gattn
+        release(PS_B_QKV);
+        PS_TL(413);
         // ---- attention over this block's key range -------------------------------------------------------------------
         if (attn_cta) {
-            ll_gather(a.qkv + (size_t)ah * HD, HD, tg + 1u, s_qh, s_abort, a.status, 72u);
-            ll_gather(a.qkv + (size_t)D + (size_t)ah * HD, HD, tg + 1u, s_qh + HD, s_abort, a.status, 72u);
-            ll_gather(a.qkv + (size_t)2 * D + (size_t)ah * HD, HD, tg + 1u, s_qh + 2 * HD, s_abort, a.status, 72u);
-            __syncthreads();
+            if (my_pages > 0) wait_full(PS_B_KV, 73u);
+            ll_gather<1>(a.qkv + (size_t)ah * HD, 3 * HD, HD, D, tg + 1u, s_qh, nullptr, nullptr, s_abort, a.status, 72u);   // q | k | v of the head
+            ps_sync();
             if (*s_abort) { live = false; break; }
-            SLLM_TL(414);
+            PS_TL(414);
             float part = 0.f;                              // thread i < HD + 2: out[i] | max | sum of this key range
             if (my_pages > 0) {
-                if (!wait_bar(PS_B_KV, 73u)) { live = false; break; }
-                SLLM_TL(415);
+                // Each warp takes a run of consecutive keys through scores, softmax weights and the value product on its
+                // own (no block barrier inside); the 16 partial results are combined once at the end.
                 const int kb = p_lo * kPage;
                 const int nk = min(my_pages * kPage, pos + 1 - kb);            // keys of this range that exist
+                const int chunk = ps_ceil_div(nk, kPsWarps);                   // <= 32 (at most 8 pages per range)
+                const int j_lo = min(nk, warp * chunk), cnt = min(nk, j_lo + chunk) - j_lo;
                 const int sub = lane % LPK, rsub = lane / LPK;
+                float* wsc = s_sc + j_lo;                                      // this warp's scores, then weights
                 float qf[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) qf[e] = s_qh[sub * 8 + e];
-                for (int j0 = warp * KPI; j0 < nk; j0 += kPsWarps * KPI) {
-                    const int j = j0 + rsub;
-                    float s = 0.f;
-                    if (j < nk) {
+#pragma unroll 2
+                for (int i0 = 0; i0 < cnt; i0 += KPI) {
+                    const int i = i0 + rsub, j = j_lo + i;
+                    float sc = 0.f;
+                    if (i < cnt) {
                         if (kb + j == pos) {               // the new key: its cache row is being written right now
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) s += qf[e] * s_qh[HD + sub * 8 + e];
+                            for (int e = 0; e < 8; ++e) sc += qf[e] * s_qh[HD + sub * 8 + e];
                         } else {
                             const __nv_bfloat16* kr = s_kv + (size_t)(2 * (j / kPage)) * page_elems + (size_t)(j % kPage) * HD + sub * 8;
                             float kf[8];
                             unpack16<__nv_bfloat16>(*reinterpret_cast<const uint4*>(kr), kf);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) s += qf[e] * kf[e];
+                            for (int e = 0; e < 8; ++e) sc += qf[e] * kf[e];
                         }
                     }
 #pragma unroll
-                    for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                    if (sub == 0 && j < nk) s_sc[j] = s * m.scale;
+                    for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+                    if (sub == 0 && i < cnt) wsc[i] = sc * m.scale;
                 }
-                __syncthreads();
-                float mx = -INFINITY;                      // every warp finds the range's maximum for itself
-                for (int j = lane; j < nk; j += 32) mx = fmaxf(mx, s_sc[j]);
-                mx = warp_max(mx);
-                const int dp = tid % DP, kg = tid / DP;
-                float o0 = 0.f, o1 = 0.f, lsum = 0.f;
-                for (int j = kg; j < nk; j += KG) {
-                    const float p = expf(s_sc[j] - mx);
-                    float w0, w1;
-                    if (kb + j == pos) { w0 = s_qh[2 * HD + 2 * dp]; w1 = s_qh[2 * HD + 2 * dp + 1]; }
-                    else {
-                        const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(
-                            s_kv + (size_t)(2 * (j / kPage) + 1) * page_elems + (size_t)(j % kPage) * HD + 2 * dp);
-                        w0 = __low2float(vv); w1 = __high2float(vv);
+                __syncwarp();
+                PS_TL(4141);
+                const float sv = lane < cnt ? wsc[lane] : -INFINITY;
+                const float mw = warp_max(sv);
+                const float pw = lane < cnt ? __expf(sv - mw) : 0.f;
+                const float lw = warp_sum(pw);
+                if (lane < cnt) wsc[lane] = pw;
+                __syncwarp();
+                PS_TL(4142);
+                constexpr int DL = HD >= 32 ? HD / 32 : 1;                     // value dims per lane
+                const bool owns = lane * DL < HD;
+                float ov[DL];
+#pragma unroll
+                for (int e = 0; e < DL; ++e) ov[e] = 0.f;
+                const int i_new = pos - kb - j_lo;                             // the new key's place in this warp's run, if it is there
+                if (owns) {
+#pragma unroll 4
+                    for (int i = 0; i < cnt; ++i) {
+                        const int j = j_lo + i;
+                        const float pj = i == i_new ? 0.f : wsc[i];            // its cache row is not final yet (it holds finite values)
+                        const __nv_bfloat16* vr = s_kv + (size_t)(2 * (j / kPage) + 1) * page_elems + (size_t)(j % kPage) * HD + lane * DL;
+                        if (DL == 1) ov[0] += pj * __bfloat162float(vr[0]);
+                        else {
+#pragma unroll
+                            for (int e = 0; e < DL; e += 2) {
+                                const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(vr + e);
+                                ov[e] += pj * __low2float(vv); ov[e + 1] += pj * __high2float(vv);
+                            }
+                        }
                     }
-                    lsum += p; o0 += p * w0; o1 += p * w1;
+                    if (i_new >= 0 && i_new < cnt) {
+                        const float pj = wsc[i_new];
+#pragma unroll
+                        for (int e = 0; e < DL; ++e) ov[e] += pj * s_qh[2 * HD + lane * DL + e];
+                    }
                 }
-                s_redo[kg * (HD + 1) + 2 * dp] = o0;
-                s_redo[kg * (HD + 1) + 2 * dp + 1] = o1;
-                if (dp == 0) s_redo[kg * (HD + 1) + HD] = lsum;
-                __syncthreads();
-                if (tid < HD) { for (int g = 0; g < KG; ++g) part += s_redo[g * (HD + 1) + tid]; }
-                else if (tid == HD) part = mx;
-                else if (tid == HD + 1) { for (int g = 0; g < KG; ++g) part += s_redo[g * (HD + 1) + HD]; }
+                float* wp = s_redo + (size_t)warp * (HD + 2);                  // [warp][out | max | sum]
+                if (owns) {
+#pragma unroll
+                    for (int e = 0; e < DL; ++e) wp[lane * DL + e] = ov[e];
+                }
+                if (lane == 0) { wp[HD] = cnt > 0 ? mw : -INFINITY; wp[HD + 1] = lw; }
+                PS_TL(4143);
+                ps_sync();
+                PS_TL(4144);
+                release(PS_B_KV);                          // s_kv is free: the next layer's pages may come
+                if (tid < kPsWarps) {                      // weight of every warp's partial result
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < kPsWarps; ++w) mx = fmaxf(mx, s_redo[w * (HD + 2) + HD]);
+                    const float mr = s_redo[tid * (HD + 2) + HD];
+                    s_sc[tid] = mr == -INFINITY ? 0.f : __expf(mr - mx);
+                    if (tid == 0) s_sc[kPsWarps] = mx;
+                }
+                ps_sync();
+                if (tid == HD) part = s_sc[kPsWarps];
+                else if (tid < HD + 2) {                   // combine the warps in warp order
+                    const int col = tid < HD ? tid : HD + 1;
+#pragma unroll
+                    for (int w = 0; w < kPsWarps; ++w) part += s_sc[w] * s_redo[w * (HD + 2) + col];
+                }
             } else if (tid == HD) {
                 part = -INFINITY;                          // an empty range: ignored by the merge
             }
             if (tid < HD + 2) ll_st(a.ap + ((size_t)(ah * S + as) * (HD + 2) + tid), part, tg + 2u);
-            __syncthreads();                               // s_kv is free: fetch the next layer's pages
-            SLLM_TL(416);
-            if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_kv(l + 1); }
+            PS_TL(416);
         }
         // ---- merge the key ranges of every head (in range order), out-projection rows, residual --------------------
-        ll_gather(a.ap, H * S * (HD + 2), tg + 2u, s_ap, s_abort, a.status, 74u);
-        __syncthreads();
+        wait_full(PS_B_O, 75u);
+        ll_gather<4>(a.ap, H * S * (HD + 2), H * S * (HD + 2), 0, tg + 2u, s_ap, nullptr, nullptr, s_abort, a.status, 74u);
+        ps_sync();
         if (*s_abort) { live = false; break; }
-        SLLM_TL(417);
-        for (int t = tid; t < D; t += kPsThreads) {
-            const int h = t / HD, d = t - h * HD;
+        PS_TL(417);
+        if (tid < H * S) {                                 // weight of every key range in its head's result: exp(max_r - max) / sum
+            const int h = tid / S;
             const float* ph = s_ap + (size_t)h * S * (HD + 2);
             float mx = -INFINITY;
-            for (int s = 0; s < S; ++s) mx = fmaxf(mx, ph[s * (HD + 2) + HD]);
-            float num = 0.f, den = 0.f;
-            for (int s = 0; s < S; ++s) {
-                const float mr = ph[s * (HD + 2) + HD];
-                if (mr == -INFINITY) continue;
-                const float w = expf(mr - mx);
-                den += w * ph[s * (HD + 2) + HD + 1];
-                num += w * ph[s * (HD + 2) + d];
+#pragma unroll 4
+            for (int r = 0; r < S; ++r) mx = fmaxf(mx, ph[r * (HD + 2) + HD]);
+            float den = 0.f;
+#pragma unroll 4
+            for (int r = 0; r < S; ++r) {
+                const float mr = ph[r * (HD + 2) + HD];
+                den += (mr == -INFINITY ? 0.f : __expf(mr - mx)) * ph[r * (HD + 2) + HD + 1];
             }
-            s_att[t] = num / den;
+            const float mine = s_ap[(size_t)tid * (HD + 2) + HD];
+            s_sc[tid] = mine == -INFINITY ? 0.f : __fdividef(__expf(mine - mx), den);
         }
-        if (!wait_bar(PS_B_O, 75u)) { live = false; break; }      // its barrier also publishes s_att
-        SLLM_TL(418);
+        PS_TL(4171);
+        ps_sync();
+        PS_TL(4172);
+        for (int t = tid; t < D; t += kPsThreads) {
+            const int h = t / HD, d = t - h * HD;
+            float acc = 0.f;
+#pragma unroll 4
+            for (int r = 0; r < S; ++r) acc += s_sc[h * S + r] * s_ap[(size_t)(h * S + r) * (HD + 2) + d];
+            s_att[t] = acc;
+        }
+        PS_TL(4173);
+        ps_sync();
+        PS_TL(418);
         for (int r = warp; r < nx; r += kPsWarps) {
             const float y = ps_dot(s_wo + (size_t)r * D, s_att, D);
             if (lane == 0) ll_st(a.xb + d0 + r, xraw[d0 + r] + y, tg + 3u);
         }
-        __syncthreads();
-        SLLM_TL(419);
-        if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_o(l + 1); }
-        // ---- x after the attention half, norm, this block's hidden units ---------------------------------------------
-        ll_gather(a.xb, D, tg + 3u, xraw, s_abort, a.status, 76u);
-        __syncthreads();
+        ps_sync();
+        release(PS_B_O);
+        PS_TL(419);
+        // ---- x after the attention half with the FFN norm's gain product, this block's hidden units ----------------
+        wait_full(PS_B_GU, 77u);
+        ss = ll_gather<4>(a.xb, D, D, 0, tg + 3u, xraw, s_gffn, xg, s_abort, a.status, 76u);
+        inv = ps_inv_rms(ss, s_red, D, m.eps);
         if (*s_abort) { live = false; break; }
-        SLLM_TL(420);
-        if (!wait_bar(PS_B_GU, 77u)) { live = false; break; }
-        ps_norm(xraw, s_gffn, xn, s_red, D, m.eps);
-        SLLM_TL(421);
+        PS_TL(421);
         for (int u = warp; u < nu; u += kPsWarps) {
             float g, up;
-            ps_dot2(s_wgu + (size_t)(2 * u) * D, s_wgu + (size_t)(2 * u + 1) * D, xn, D, g, up);
+            ps_dot2(s_wgu + (size_t)(2 * u) * D, s_wgu + (size_t)(2 * u + 1) * D, xg, D, g, up);
             if (lane == 0) {                               // silu(g) * up, src/nn/swiglu.cpp:37-57
+                g *= inv; up *= inv;
                 const float sig = 1.0f / (1.0f + expf(-g));
                 ll_st(a.hb + u0 + u, (g * sig) * up, tg + 4u);
             }
         }
-        __syncthreads();
-        SLLM_TL(422);
-        if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_gu(l + 1); }
+        ps_sync();
+        release(PS_B_GU);
+        PS_TL(422);
         // ---- all hidden units, down-projection rows, residual -----------------------------------------------------------
-        ll_gather(a.hb, F, tg + 4u, s_hid, s_abort, a.status, 78u);
-        __syncthreads();
+        wait_full(PS_B_D, 79u);
+        ll_gather<4>(a.hb, F, F, 0, tg + 4u, s_hid, nullptr, nullptr, s_abort, a.status, 78u);
+        ps_sync();
         if (*s_abort) { live = false; break; }
-        SLLM_TL(423);
-        if (!wait_bar(PS_B_D, 79u)) { live = false; break; }
-        SLLM_TL(424);
+        PS_TL(424);
         for (int r = warp; r < nx; r += kPsWarps) {
             const float y = ps_dot(s_wd + (size_t)r * F, s_hid, F);
             if (lane == 0) {
@@ -526,51 +678,31 @@ __global__ void __launch_bounds__(kPsThreads, 1) k_decode_persist(const PersistA
                 if (l + 1 == NL && a.logits == nullptr) a.x_out[d0 + r] = xnew;
             }
         }
-        __syncthreads();
-        SLLM_TL(425);
-        if (l + 1 < NL) { if (tid == 0) ps_fence_async(); issue_d(l + 1); }
+        ps_sync();
+        release(PS_B_D);
+        PS_TL(425);
     }
 
-    // ---- final norm and the tied head: this block's vocabulary rows streamed through the freed weight buffers ------
+    // ---- final norm and the tied head: this block's vocabulary rows, streamed through shared memory --------------
     if (live && a.logits != nullptr) {
-        const uint32_t stage_bytes = (uint32_t)kPsHeadRows * D * 2;
-        const int n_rows = v1 - v0, n_st = ps_ceil_div(n_rows, kPsHeadRows), ns = lay.head_stages;
-        auto issue_head = [&](int st) {
-            if (tid == 0) {
-                const int rows = min(kPsHeadRows, n_rows - st * kPsHeadRows);
-                const uint32_t bytes = (uint32_t)rows * D * 2;
-                ps_expect(BAR(PS_B_HEAD + st % ns), bytes);
-                ps_bulk(ps_smem(smem + lay.o_wqkv) + (uint32_t)(st % ns) * stage_bytes, a.emb_w + (size_t)(v0 + st * kPsHeadRows) * D, bytes,
-                        BAR(PS_B_HEAD + st % ns));
-            }
-        };
-        if (tid == 0) ps_fence_async();
-        int issued = 0;
-        for (; issued < min(ns, n_st); ++issued) issue_head(issued);
-        ll_gather(a.xa, D, epoch * 1024u + (uint32_t)NL * 8u, xraw, s_abort, a.status, 80u);
-        __syncthreads();
-        bool go = *s_abort == 0;
-        SLLM_TL(430);
-        if (go) ps_norm(xraw, s_gfinal, xn, s_red, D, m.eps);
-        for (int st = 0; st < issued; ++st) {              // after a failure nothing more is issued: the loop drains
-            const bool ok = mbar_wait_bounded(BAR(PS_B_HEAD + st % ns), (uint32_t)((st / ns) & 1), c_wait_limit_ns);
+        ss = ll_gather<4>(a.xa, D, D, 0, epoch * 1024u + (uint32_t)NL * 8u, xraw, s_gfinal, xg, s_abort, a.status, 80u);
+        inv = ps_inv_rms(ss, s_red, D, m.eps);
+        PS_TL(430);
+        for (int st = 0; st < n_st && *s_abort == 0; ++st) {
+            const bool ok = mbar_wait_bounded(FULL(PS_B_HEAD + st % ns), (uint32_t)((st / ns) & 1), c_wait_limit_ns);
             if (!ok) { *s_abort = 1; atomicExch(a.status, 81u); }
-            const int row = st * kPsHeadRows + warp;
-            if (go && ok && row < n_rows) {
-                const float y = ps_dot(reinterpret_cast<const __nv_bfloat16*>(smem + lay.o_wqkv + (size_t)(st % ns) * stage_bytes) + (size_t)warp * D, xn, D);
-                if (lane == 0) a.logits[v0 + row] = y;
+            const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(head_slot(st % ns)) + (size_t)(2 * warp) * D;
+            const int row = st * kPsHeadRows + 2 * warp;
+            if (ok && row < n_head_rows) {
+                float y0, y1;
+                ps_dot2(w, row + 1 < n_head_rows ? w + D : w, xg, D, y0, y1);
+                if (lane == 0) { a.logits[v0 + row] = y0 * inv; if (row + 1 < n_head_rows) a.logits[v0 + row + 1] = y1 * inv; }
             }
-            __syncthreads();
-            go = go && *s_abort == 0;
-            if (go && issued < n_st) { if (tid == 0) ps_fence_async(); issue_head(issued); ++issued; }
+            ps_sync();
+            if (tid == 0) ps_arrive(FREE(PS_B_HEAD + st % ns));
         }
-    } else {
-        // a wait ran out (or an earlier kernel's did): let this block's copies in flight land before its shared
-        // memory is given to another block
-        for (int b = 0; b < 5; ++b)
-            while (n_waited[b] < n_issued[b]) { mbar_wait_bounded(BAR(b), (uint32_t)(n_waited[b] & 1), c_wait_limit_ns); n_waited[b] += 1; }
     }
-    SLLM_TL(432);
+    PS_TL(432);
     if (cta == 0 && tid == 0) *a.epoch = epoch + 1u;
 }
 

@@ -594,7 +594,7 @@ int launch_attn_any(sllm_engine* e, const AttnDecArgs& t, bool pdl) { return lau
 
 template <int HD>
 int launch_persist_hd(sllm_engine* e, const PersistArgs& a, bool pdl) {
-    return launch(e, k_decode_persist<HD>, dim3(a.na), dim3(kPsThreads), e->ps_smem, pdl, a);
+    return launch(e, k_decode_persist<HD>, dim3(a.na), dim3(kPsBlock), e->ps_smem, pdl, a);
 }
 
 // One token through every layer and the head as a single resident kernel.
@@ -607,7 +607,7 @@ int run_pass_persist(sllm_engine* e, const PassView& pv, int n_rows, float* logi
     a.xa = e->ps_xa; a.xb = e->ps_xb; a.qkv = e->ps_qkv; a.ap = e->ps_ap; a.hb = e->ps_hb;
     a.epoch = e->ps_epoch; a.status = e->d_status;
     a.logits = n_rows > 0 ? logits : nullptr; a.x_out = e->x;
-    a.na = e->ps_na; a.s_max = e->ps_smax; a.pps_max = e->ps_ppsmax;
+    a.na = e->ps_na; a.s_max = e->ps_smax; a.pps_max = e->ps_ppsmax; a.smem_total = (uint32_t)e->ps_smem;
     switch (e->md.hd) {
         case 16: return launch_persist_hd<16>(e, a, pdl);
         case 32: return launch_persist_hd<32>(e, a, pdl);
@@ -1320,9 +1320,10 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             if (na >= (int)H && L <= 120) {
                 const int s_max = na / (int)H;
                 const int pps_max = std::max(2, (e->pages_per_seq + s_max - 1) / s_max);
-                const PsLayout lay = ps_layout(m, na, s_max, pps_max, e->pages_per_seq);
-                if (lay.total <= e->max_dyn_smem && lay.head_stages >= 2) {
-                    e->ps_na = na; e->ps_smax = s_max; e->ps_ppsmax = pps_max; e->ps_smem = lay.total;
+                // the launch takes all the shared memory an SM offers: what the layers leave free holds early head stages
+                const PsLayout lay = ps_layout(m, na, s_max, pps_max, e->pages_per_seq, (uint32_t)e->max_dyn_smem);
+                if (lay.total <= e->max_dyn_smem && lay.head_stages + lay.head_pre >= 2 && pps_max <= 8) {
+                    e->ps_na = na; e->ps_smax = s_max; e->ps_ppsmax = pps_max; e->ps_smem = e->max_dyn_smem;
                     A(&e->ps_xa, D, &e->scratch_bytes); A(&e->ps_xb, D, &e->scratch_bytes);
                     A(&e->ps_qkv, 3 * D, &e->scratch_bytes);
                     A(&e->ps_ap, (size_t)H * s_max * (hd + 2), &e->scratch_bytes);
@@ -1336,10 +1337,10 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
                         cudaStreamSynchronize(e->stream);
                         cudaError_t ce = cudaSuccess;
                         switch (hd) {
-                            case 16: ce = cudaFuncSetAttribute(k_decode_persist<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
-                            case 32: ce = cudaFuncSetAttribute(k_decode_persist<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
-                            case 64: ce = cudaFuncSetAttribute(k_decode_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
-                            default: ce = cudaFuncSetAttribute(k_decode_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total); break;
+                            case 16: ce = cudaFuncSetAttribute(k_decode_persist<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->ps_smem); break;
+                            case 32: ce = cudaFuncSetAttribute(k_decode_persist<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->ps_smem); break;
+                            case 64: ce = cudaFuncSetAttribute(k_decode_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->ps_smem); break;
+                            default: ce = cudaFuncSetAttribute(k_decode_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->ps_smem); break;
                         }
                         if (ce != cudaSuccess) { e->err = "cudaFuncSetAttribute failed for the persistent decode kernel"; rc = SLLM_ERR_CUDA; }
                         else e->persist_ok = true;
@@ -1709,6 +1710,12 @@ int sllm_slot_release(sllm_engine* e, uint32_t slot) {
 }
 
 uint32_t sllm_num_live(const sllm_engine* e) { return e ? (uint32_t)e->n_live : 0; }
+
+int sllm_engine_make_current(sllm_engine* e) {
+    if (!e) return SLLM_ERR_INVALID;
+    CU(cudaSetDevice(e->dev));
+    return SLLM_OK;
+}
 
 int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n) {
     if (!e || !flags || n > (uint32_t)e->max_batch) return fail(e, SLLM_ERR_INVALID, "sllm_get_finished: bad argument");
