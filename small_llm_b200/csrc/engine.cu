@@ -1809,7 +1809,7 @@ static int generate_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* le
     // A slot's token buffer holds 2 * context_length + 2 ids: a request that could outgrow it is refused here rather
     // than cut short without notice (the reference slides its window without bound).
     for (uint32_t s = 0; s < n_seq && s < (uint32_t)e->max_batch; ++s)
-        if ((uint64_t)lens[s] + max_new > (uint64_t)e->st.tok_cap)
+        if (lens[s] < (uint32_t)e->st.tok_cap && (uint64_t)lens[s] + max_new > (uint64_t)e->st.tok_cap)    // longer prompts: refused below
             return fail(e, SLLM_ERR_CAPACITY, "sllm_generate: prompt plus max_new_tokens exceed a slot's token buffer "
                                               "(2 * context_length + 2)");
     rc = load_slots(e, ids, lens, n_seq, /*allow_long=*/true);

@@ -138,6 +138,25 @@ def test_config2_sampled_512_steps(fp32, tol):
     assert np.array_equal(free[:n_prompt + same], ref[:n_prompt + same])
 
 
+def _greedy_stream_against_oracle(eng, o, st, n0):
+    """Teacher-forced check of one engine-generated greedy stream st (prompt of n0 ids + continuation): returns
+    (steps checked, worst logits rel err, all flips, flips at a reference margin >= 1e-2 with the logit error there).
+    The engine's own logits for the stream come from one all-positions forward."""
+    T = len(st) - 1
+    ref = o.forward(st[:T], 1, T, row_from=n0 - 1)[0]
+    got = eng.forward_logits(st[:T], 1, T)[0][n0 - 1:]
+    err = np.abs(got - ref).max(axis=1)
+    worst = float((err / np.abs(ref).max(axis=1)).max())
+    flips, wide = [], []
+    for i in range(T - n0 + 1):
+        want, margin = greedy(ref[i], st[: n0 + i], 1.0)
+        if int(st[n0 + i]) != want:
+            flips.append((i, margin))
+            if margin >= 1e-2:
+                wide.append((i, margin, float(err[i])))
+    return T - n0 + 1, worst, flips, wide
+
+
 def _config4_prompts(n_seq):
     """Benchmark config 4: prompt lengths uniform in [256, 1536] from seed 4 (mt19937(4)() % 1281 + 256), ids from the
     same generator family (one seed per sequence keeps the sequences independent)."""
@@ -188,19 +207,11 @@ def test_config4_batch512_ragged_to_full_context():
     flips, wide, checked, worst = [], [], 0, 0.0
     for s in sorted(picks):
         st = streams[s][: cfg.context + 1]
-        T = min(len(st) - 1, cfg.context)
-        n0 = int(lens[s])
-        ref = o.forward(st[:T], 1, T, row_from=n0 - 1)[0]
-        got = eng.forward_logits(st[:T], 1, T)[0][n0 - 1:]                # the engine's own logits, teacher-forced
-        err = np.abs(got - ref).max(axis=1)
-        worst = max(worst, float((err / np.abs(ref).max(axis=1)).max()))
-        for i in range(T - n0 + 1):
-            want, margin = greedy(ref[i], st[: n0 + i], 1.0)
-            checked += 1
-            if int(st[n0 + i]) != want:
-                flips.append((s, i, margin))
-                if margin >= 1e-2:
-                    wide.append((s, i, margin, float(err[i])))
+        n, w, fl, wd = _greedy_stream_against_oracle(eng, o, st, int(lens[s]))
+        checked += n
+        worst = max(worst, w)
+        flips += [(s,) + f for f in fl]
+        wide += [(s,) + f for f in wd]
     print(f"config 4: eos id {eos}, {len(retired)} sequences retired early, {checked} steps checked on sequences "
           f"{sorted(picks)}, worst logits rel err {worst:.2e}, {len(flips)} arg-max flips, {len(wide)} of them at a "
           f"reference margin of 1e-2 or more: {wide}")
@@ -216,8 +227,9 @@ def test_config4_batch512_ragged_to_full_context():
 
 def test_config5_full_depth():
     """Benchmark config 5's model as specified -- 24 layers, d_model 1536, 24 heads of 64, SwiGLU 4096, vocabulary
-    32768, seed-5 N(0,0.02) weights, bf16 -- on two sequences with prompts of 1024 ids: logits of the last prompt
-    position and of 16 greedy decode steps against the oracle."""
+    32768, seed-5 N(0,0.02) weights, bf16 -- on two sequences with prompts of 1024 ids: the logits of the last prompt
+    position and of each of 16 greedy decode steps (read back step by step) against the oracle; greedy tokens by the
+    rule of the config-4 test."""
     cfg = Config(vocab=32768, context=2048, layers=24, d_model=1536, heads=24, ffn=4096)
     n_prompt, n_new = 1024, 16
     o, eng = make_pair(cfg, seed=5, stddev=0.02, fp32=False, max_batch=2, via_checkpoint=False)
@@ -225,19 +237,29 @@ def test_config5_full_depth():
     prompts = [ids[:n_prompt], ids[n_prompt:]]
     opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
     eng.prefill(prompts)
-    first = [eng.step_logits(s) for s in range(2)]
-    eng.decode_loop(n_new, opt, None, eos=cfg.vocab + 1)
-    last = [eng.step_logits(s) for s in range(2)]
-    flips = []
+    step_logits = [[], []]                                   # the decode path's own logits at every step
+    for i in range(n_new + 1):
+        for s in range(2):
+            step_logits[s].append(eng.step_logits(s))
+        if i < n_new:
+            eng.sample(opt, eos=cfg.vocab + 1)
+            eng.decode_step()
+    flips, wide, worst = [], [], 0.0
     for s in range(2):
         st = eng.tokens(s)
         assert st.size == n_prompt + n_new
         ref = o.forward(st, 1, st.size, row_from=n_prompt - 1)[0]
-        assert rel_err(first[s], ref[0]) <= TOL_BF16
-        assert rel_err(last[s], ref[n_new]) <= TOL_BF16
+        got = np.stack(step_logits[s])
+        err = np.abs(got - ref).max(axis=1)
+        worst = max(worst, float((err / np.abs(ref).max(axis=1)).max()))
         for i in range(n_new):
             want, margin = greedy(ref[i], st[: n_prompt + i], 1.0)
             if int(st[n_prompt + i]) != want:
                 flips.append((s, i, margin))
-    assert all(m < 1e-2 for *_, m in flips), flips
-    assert len(flips) <= 3, flips
+                if margin >= 1e-2:
+                    wide.append((s, i, margin, float(err[i])))
+    print(f"config 5: worst logits rel err over {2 * (n_new + 1)} decode steps {worst:.2e}, flips {flips}, at a margin of 1e-2 or more: {wide}")
+    # same rule as for config 4: below the 1e-2 margin, or explained by the logit error measured at that step
+    assert worst <= TOL_BF16
+    assert all(m <= 2.5 * e for _, _, m, e in wide), wide
+    assert len(flips) <= 4 and len(wide) <= 2, (flips, wide)
