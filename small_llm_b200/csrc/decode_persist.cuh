@@ -22,7 +22,7 @@
 //     waits (bounded) for its own copies in flight and returns; the others run into the same limit.
 //
 // Measured and dropped: requesting every polled word three times 0.15 us apart (slower: 354 against 329 us per token
-// on the same GPU), splitting a down-projection row over several warps (two more block barriers cost more than the
+// on the same GPU), sleeping 50-300 ns between two polls of a word (284 -> 364-383 us), splitting a down-projection row over several warps (two more block barriers cost more than the
 // shorter sums saved).
 //
 // Buffers are reused by every layer.  That is safe because the hand-offs of x and of the hidden units are

@@ -1314,7 +1314,10 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
         }
         // persistent single-token decode: every block of the grid must own rows of every product, and its slices fit
         if (!rc && std::getenv("SLLM_NO_PERSIST") == nullptr) {
-            int nc = e->sm_count;
+            // Not every SM: measured on a 148-SM part, 124-132 blocks give 257-260 us per token against 272-275 us with
+            // 136-148 (and 290 us with 104): the sampler kernels between two tokens, and the next token's blocks that
+            // start early, find free SMs instead of queueing behind blocks that hold all of an SM's shared memory.
+            int nc = e->sm_count > 40 ? e->sm_count - 20 : e->sm_count;
             if (const char* v = std::getenv("SLLM_PERSIST_CTAS")) nc = std::max(1, std::min(nc, std::atoi(v)));
             const int na = (int)std::min<uint64_t>({(uint64_t)nc, D, F, 3 * D / 2});
             if (na >= (int)H && L <= 120) {
