@@ -34,6 +34,7 @@
 // and accumulation, bf16 weights and KV cache.
 #pragma once
 #include "common.cuh"
+#include "sampler.cuh"
 
 namespace sllm {
 
@@ -67,13 +68,20 @@ struct PersistArgs {
     int s_max;                           // key ranges per head at most (na / H)
     int pps_max;                         // KV pages per key range at most
     uint32_t smem_total;                 // dynamic shared memory of the launch
+    // The first two kernels of the sampler that follows (k_samp_max, k_samp_hist) done here, by the blocks that hold
+    // the logits: per-block first maximum of the penalised scores, the slot's maximum (one more hand-off), the weights
+    // expf((s - max) / T) and their level-0 histogram.  Off when fold_temperature < 0.
+    float fold_temperature, fold_penalty;
+    SeqState st;
+    unsigned long long* g_mass; unsigned int* g_cnt; float* g_w; float* g_pmax_val; int* g_pmax_idx;
+    unsigned long long* mxb;             // [2 * na] tagged words: every block's (maximum, index)
 };
 
 // ---- shared-memory layout, the same arithmetic on host and device ---------------------------------------------
 struct PsLayout {
     int rq, rx, ru;                      // most QKV rows, residual rows, hidden units of any block
     uint32_t o_wqkv, o_wo, o_wgu, o_wd, o_kv, o_region_end;      // [o_wqkv, o_region_end) is reused by the head stages
-    uint32_t o_gattn, o_gffn, o_gfinal, o_xraw, o_xn, o_att, o_hid, o_ap, o_sc, o_qh, o_redo, o_rope, o_pages, o_red, o_bars, o_head_pre;
+    uint32_t o_gattn, o_gffn, o_gfinal, o_xraw, o_xn, o_att, o_hid, o_ap, o_sc, o_qh, o_redo, o_rope, o_pages, o_red, o_bars, o_logits, o_head_pre;
     uint32_t total;                      // bytes the layers need; the head's early stages take what is left of smem_total
     int head_stages, head_pre;
 };
@@ -106,6 +114,7 @@ __host__ __device__ inline PsLayout ps_layout(const ModelDims& m, int na, int s_
     L.o_pages = o;  o = ps_align(o + (uint32_t)pages_per_seq * 4);
     L.o_red = o;    o = ps_align(o + 64 * 4);
     L.o_bars = o;   o = ps_align(o + 2 * (5 + kPsMaxHeadStages) * 8);
+    L.o_logits = o; o = ps_align(o + (uint32_t)ps_ceil_div(m.V, na) * 4);
     L.o_head_pre = o;
     L.total = o;
     const uint32_t stage = (uint32_t)kPsHeadRows * m.D * 2;
@@ -288,6 +297,7 @@ __global__ void __launch_bounds__(kPsBlock, 1) k_decode_persist(const PersistArg
     float2* s_rope = reinterpret_cast<float2*>(smem + lay.o_rope);
     int* s_pages = reinterpret_cast<int*>(smem + lay.o_pages);
     float* s_red = reinterpret_cast<float*>(smem + lay.o_red);
+    float* s_logits = reinterpret_cast<float*>(smem + lay.o_logits);   // this block's logits, for the folded sampler kernels
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_red + 32);
     const uint32_t bar0 = ps_smem(smem + lay.o_bars);
     auto FULL = [&](int i) { return bar0 + 8u * (uint32_t)i; };                   // "the copy has landed"
@@ -696,10 +706,58 @@ __global__ void __launch_bounds__(kPsBlock, 1) k_decode_persist(const PersistArg
             if (ok && row < n_head_rows) {
                 float y0, y1;
                 ps_dot2(w, row + 1 < n_head_rows ? w + D : w, xg, D, y0, y1);
-                if (lane == 0) { a.logits[v0 + row] = y0 * inv; if (row + 1 < n_head_rows) a.logits[v0 + row + 1] = y1 * inv; }
+                if (lane == 0) {
+                    a.logits[v0 + row] = y0 * inv; s_logits[row] = y0 * inv;
+                    if (row + 1 < n_head_rows) { a.logits[v0 + row + 1] = y1 * inv; s_logits[row + 1] = y1 * inv; }
+                }
             }
             ps_sync();
             if (tid == 0) ps_arrive(FREE(PS_B_HEAD + st % ns));
+        }
+        PS_TL(431);
+        // ---- the sampler's first two kernels, folded in (src/inference.cpp:104-131: penalty, maximum, weights) ----------
+        if (a.fold_temperature >= 0.f && *s_abort == 0) {
+            const float pen = a.fold_penalty;
+            const uint32_t* seen = a.st.seen + (size_t)slot * (V / 32);
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int t = tid; t < n_head_rows; t += kPsThreads) {          // ascending ids per thread: a strict > keeps the first maximum
+                const int i = v0 + t;
+                float sv = s_logits[t];
+                if (pen != 1.0f && ((seen[i >> 5] >> (i & 31)) & 1u)) sv = sv > 0.f ? sv / pen : sv * pen;
+                s_logits[t] = sv;
+                if (sv > bv) { bv = sv; bi = i; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) first_max(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+            int* s_redi = reinterpret_cast<int*>(s_red + 16);
+            if (lane == 0) { s_red[warp] = bv; s_redi[warp] = bi; }
+            ps_sync();
+            const uint32_t tgm = epoch * 1024u + (uint32_t)NL * 8u + 1u;
+            if (tid == 0) {
+                for (int w = 1; w < kPsWarps; ++w) first_max(bv, bi, s_red[w], s_redi[w]);
+                ll_st(a.mxb + 2 * cta, bv, tgm);
+                ll_st(a.mxb + 2 * cta + 1, __int_as_float(bi), tgm);
+                a.g_pmax_val[(size_t)slot * a.na + cta] = bv;               // what k_samp_pick reads: one part per block
+                a.g_pmax_idx[(size_t)slot * a.na + cta] = bi;
+            }
+            ll_gather<1>(a.mxb, 2 * a.na, 2 * a.na, 0, tgm, s_ap, nullptr, nullptr, s_abort, a.status, 83u);
+            ps_sync();
+            float mx = -INFINITY; int arg = 0x7fffffff;                     // every warp finds the slot's maximum for itself
+            for (int b = lane; b < a.na; b += 32) first_max(mx, arg, s_ap[2 * b], __float_as_int(s_ap[2 * b + 1]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) first_max(mx, arg, __shfl_xor_sync(0xffffffffu, mx, o), __shfl_xor_sync(0xffffffffu, arg, o));
+            if (a.fold_temperature > 0.f && *s_abort == 0 && a.st.finished[slot] == 0 && isfinite(mx)) {
+                float* w = a.g_w + (size_t)slot * V;
+                unsigned long long* gm = a.g_mass + (size_t)slot * kL0Buckets;
+                unsigned int* gc = a.g_cnt + (size_t)slot * kL0Buckets;
+                for (int t = tid; t < n_head_rows; t += kPsThreads) {
+                    const float e = expf((s_logits[t] - mx) / a.fold_temperature);
+                    w[v0 + t] = e;
+                    const int b = l0_bucket(__float_as_uint(e));
+                    atomicAdd(gm + b, fix_of(e));                           // results unused: reductions performed in L2
+                    atomicAdd(gc + b, 1u);
+                }
+            }
         }
     }
     PS_TL(432);

@@ -134,6 +134,8 @@ struct sllm_engine {
     size_t ps_smem = 0;
     unsigned long long *ps_xa = nullptr, *ps_xb = nullptr, *ps_qkv = nullptr, *ps_ap = nullptr, *ps_hb = nullptr;
     unsigned int* ps_epoch = nullptr;
+    unsigned long long* ps_mxb = nullptr;
+    bool fold_sampler = true;           // SLLM_NO_FOLD: the sampler's first two kernels stay kernels of their own
     LayerW* d_layers = nullptr;
     // attention scratch
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
@@ -598,8 +600,15 @@ int launch_persist_hd(sllm_engine* e, const PersistArgs& a, bool pdl) {
 }
 
 // One token through every layer and the head as a single resident kernel.
-int run_pass_persist(sllm_engine* e, const PassView& pv, int n_rows, float* logits, bool pdl) {
+int run_pass_persist(sllm_engine* e, const PassView& pv, int n_rows, float* logits, bool pdl, const SampleArgs* fold) {
     PersistArgs a{};
+    a.fold_temperature = -1.f;
+    if (fold && n_rows > 0) {                                   // the next sampling step's first two kernels ride along
+        a.fold_temperature = fold->temperature > 0.f ? fold->temperature : 0.f;
+        a.fold_penalty = fold->penalty; a.st = fold->st;
+        a.g_mass = fold->g_mass; a.g_cnt = fold->g_cnt; a.g_w = fold->g_w; a.g_pmax_val = fold->g_pmax_val; a.g_pmax_idx = fold->g_pmax_idx;
+        a.mxb = e->ps_mxb;
+    }
     a.m = e->md; a.kv = KvView{e->kv_pool, e->d_block_table, e->n_pages, e->pages_per_seq};
     a.tok_id = pv.tok_id; a.tok_slot = pv.tok_slot; a.tok_pos = pv.tok_pos;
     a.layers = e->d_layers; a.emb_f32 = e->emb_f32; a.emb_w = static_cast<const __nv_bfloat16*>(e->emb_w);
@@ -617,8 +626,12 @@ int run_pass_persist(sllm_engine* e, const PassView& pv, int n_rows, float* logi
     return fail(e, SLLM_ERR_INVALID, "unsupported head_dim");
 }
 
-int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl) {
-    if (pv.n_tok == 1 && e->persist_ok && (n_rows == 0 || row_tok == nullptr)) return run_pass_persist(e, pv, n_rows, logits, pdl);
+// Whether a decode pass over the live slots would run as the persistent single-token kernel (which can carry the next
+// sampling step's first two kernels).
+bool pass_is_persistent(const sllm_engine* e, int n_tok) { return n_tok == 1 && e->persist_ok; }
+
+int run_pass(sllm_engine* e, const PassView& pv, const int* row_tok, int n_rows, float* logits, bool pdl, const SampleArgs* fold = nullptr) {
+    if (pass_is_persistent(e, pv.n_tok) && (n_rows == 0 || row_tok == nullptr)) return run_pass_persist(e, pv, n_rows, logits, pdl, fold);
     if (pv.n_tok == 1 && e->fused_ok && (n_rows == 0 || row_tok == nullptr))
         return e->f32 ? run_pass_fused_t<float>(e, pv, n_rows, logits, pdl) : run_pass_fused_t<__nv_bfloat16>(e, pv, n_rows, logits, pdl);
     if (!e->f32 && e->encode_tiled && pv.n_tok >= e->tc_min_tokens) return run_pass_tc(e, pv, row_tok, n_rows, logits, pdl);
@@ -720,13 +733,20 @@ int configure_kernels(sllm_engine* e) {
     return e->f32 ? configure_kernels_t<float>(e) : configure_kernels_t<__nv_bfloat16>(e);
 }
 
-int launch_sampler(sllm_engine* e, const SampleArgs& s, bool pdl) {
-    const dim3 part_grid(s.bps, s.n_slots);
-    int rc = launch(e, k_samp_max, part_grid, dim3(kSampPartThreads), 0, pdl, s);
-    if (rc) return rc;
-    if (s.temperature > 0.0f) {
-        rc = launch(e, k_samp_hist, part_grid, dim3(kSampPartThreads), 0, pdl, s);
+// folded: the persistent decode kernel before this sampling step has already produced the per-part maxima (one part
+// per block of its grid), the weights and the level-0 histogram: only the pick kernel is left.
+int launch_sampler(sllm_engine* e, SampleArgs s, bool pdl, bool folded = false) {
+    int rc = SLLM_OK;
+    if (folded) {
+        s.bps = e->ps_na;
+    } else {
+        const dim3 part_grid(s.bps, s.n_slots);
+        rc = launch(e, k_samp_max, part_grid, dim3(kSampPartThreads), 0, pdl, s);
         if (rc) return rc;
+        if (s.temperature > 0.0f) {
+            rc = launch(e, k_samp_hist, part_grid, dim3(kSampPartThreads), 0, pdl, s);
+            if (rc) return rc;
+        }
     }
     const size_t smem = s.temperature > 0.0f ? (size_t)e->md.V * sizeof(float) : 16;
     return launch(e, k_samp_pick, dim3(s.n_slots), dim3(kSampThreads), smem, pdl, s);
@@ -767,11 +787,13 @@ int refresh_attn_order(sllm_engine* e) {
     return SLLM_OK;
 }
 
-// One decode iteration = sampler, then the model over the sampled tokens.
-int enqueue_iteration(sllm_engine* e, const SampleArgs& s) {
-    int rc = launch_sampler(e, s, true);
+// One decode iteration = sampler, then the model over the sampled tokens.  fold_in: the pass before this iteration
+// carried this sampler's first two kernels; fold_out: this pass carries the next sampler's.  Folding stays inside one
+// graph (the last pass of a graph never folds), so whatever follows a graph starts from a clean histogram.
+int enqueue_iteration(sllm_engine* e, const SampleArgs& s, bool fold_in = false, bool fold_out = false) {
+    int rc = launch_sampler(e, s, true, fold_in);
     if (rc) return rc;
-    return run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, true);
+    return run_pass(e, decode_view(e), nullptr, e->n_live, e->step_logits, true, fold_out ? &s : nullptr);
 }
 
 // A graph of `iters` consecutive decode iterations: inside it the head of one iteration and the sampler of the next
@@ -789,7 +811,8 @@ int get_iteration_graph(sllm_engine* e, const SampleArgs& s, int iters, cudaGrap
     const uint64_t before = e->launches;
     CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     int rc = SLLM_OK;
-    for (int i = 0; i < iters && !rc; ++i) rc = enqueue_iteration(e, s);
+    const bool can_fold = pass_is_persistent(e, e->n_live) && s.n_slots == 1 && e->ps_na <= 128 && e->fold_sampler;   // the pick kernel reads up to 128 parts
+    for (int i = 0; i < iters && !rc; ++i) rc = enqueue_iteration(e, s, can_fold && i > 0, can_fold && i + 1 < iters);
     cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
     e->iter_launches = (int)(e->launches - before);
     e->launches = before;
@@ -1318,6 +1341,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
             // 136-148 (and 290 us with 104): the sampler kernels between two tokens, and the next token's blocks that
             // start early, find free SMs instead of queueing behind blocks that hold all of an SM's shared memory.
             int nc = e->sm_count > 40 ? e->sm_count - 20 : e->sm_count;
+            e->fold_sampler = std::getenv("SLLM_NO_FOLD") == nullptr;
             if (const char* v = std::getenv("SLLM_PERSIST_CTAS")) nc = std::max(1, std::min(nc, std::atoi(v)));
             const int na = (int)std::min<uint64_t>({(uint64_t)nc, D, F, 3 * D / 2});
             if (na >= (int)H && L <= 120) {
@@ -1332,6 +1356,7 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
                     A(&e->ps_ap, (size_t)H * s_max * (hd + 2), &e->scratch_bytes);
                     A(&e->ps_hb, F, &e->scratch_bytes);
                     A(&e->ps_epoch, 4, &e->scratch_bytes);
+                    A(&e->ps_mxb, 2 * (size_t)na, &e->scratch_bytes);
                     A(&e->d_layers, L, &e->scratch_bytes);
                     if (!rc) {
                         const unsigned int one = 1;
@@ -1731,33 +1756,40 @@ int sllm_get_finished(sllm_engine* e, int32_t* flags, uint32_t n) {
 static int decode_loop_impl(sllm_engine* e, uint64_t n_steps, const sllm_sampling* opt, const double* d_draws, int stride,
                             int seeded, bool last_pass, bool* all_done_out) {
     SampleArgs s = make_sample_args(e, opt, e->n_live, d_draws, stride, seeded);
-    cudaGraphExec_t ge = nullptr, ge_multi = nullptr;
-    constexpr uint64_t kMulti = 8, check_every = 64;           // kMulti divides check_every
-    int launches_one = 0, launches_multi = 0;
+    cudaGraphExec_t ge = nullptr, ge_multi[2] = {nullptr, nullptr};
+    constexpr uint64_t kMulti[2] = {32, 8}, check_every = 64;  // both divide check_every
+    int launches_one = 0, launches_multi[2] = {0, 0};
     { int rc = refresh_attn_order(e); if (rc) return rc; }
     if (e->opt.use_graph) {
-        int rc = get_iteration_graph(e, s, 1, &ge);
-        if (rc) return rc;
-        launches_one = launches_per_iteration(e);
-        if (n_steps > kMulti) {
-            rc = get_iteration_graph(e, s, (int)kMulti, &ge_multi);
+        // graphs of 32 and of 8 iterations: inside a graph consecutive kernels are joined by programmatic edges, and the
+        // batch-1 kernel carries the next sampling step's first two kernels
+        for (int attempt = 0; attempt < 2; ++attempt) {           // inserting a graph may empty the cache (cleared past 32 entries): fetch again
+            int rc = get_iteration_graph(e, s, 1, &ge);
             if (rc) return rc;
-            launches_multi = launches_per_iteration(e);
-            // inserting a graph may have emptied the cache (it is cleared when it grows past 32 entries)
-            rc = get_iteration_graph(e, s, 1, &ge);
-            if (rc) return rc;
+            launches_one = launches_per_iteration(e);
+            for (int k = 0; k < 2; ++k) {
+                ge_multi[k] = nullptr;
+                if (n_steps > kMulti[k]) {
+                    rc = get_iteration_graph(e, s, (int)kMulti[k], &ge_multi[k]);
+                    if (rc) return rc;
+                    launches_multi[k] = launches_per_iteration(e);
+                }
+            }
         }
     }
     const uint64_t full_steps = last_pass ? n_steps : n_steps - 1;     // the last step of a generate call only samples
     uint64_t i = 0;
     while (i < n_steps) {
         uint64_t done = 1;
-        if (ge_multi && i % kMulti == 0 && i + kMulti <= full_steps) {
-            for (uint64_t k = 0; k < kMulti; ++k) { int rc = grow_for_step(e); if (rc) return rc; }
-            CU(cudaGraphLaunch(ge_multi, e->stream));
-            e->launches += launches_multi;
-            e->decode_steps += kMulti;
-            done = kMulti;
+        int m = -1;
+        for (int k = 0; k < 2 && m < 0; ++k)
+            if (ge_multi[k] && i % kMulti[k] == 0 && i + kMulti[k] <= full_steps) m = k;
+        if (m >= 0) {
+            for (uint64_t k = 0; k < kMulti[m]; ++k) { int rc = grow_for_step(e); if (rc) return rc; }
+            CU(cudaGraphLaunch(ge_multi[m], e->stream));
+            e->launches += launches_multi[m];
+            e->decode_steps += kMulti[m];
+            done = kMulti[m];
         } else {
             int rc = grow_for_step(e);
             if (rc) return rc;

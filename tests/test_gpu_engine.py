@@ -430,3 +430,23 @@ def test_persistent_decode_kernel_against_oracle_and_layerwise_kernels(cfg, std,
         rl = o.forward(got[:first], 1, first)[0, -1]
         _, margin = greedy(rl, got[:first], 1.0)
         assert margin < 1e-2, (first, margin)
+
+
+@pytest.mark.parametrize("t,p,pen", [(0.8, 0.95, 1.15), (1.0, 0.5, 1.0), (0.0, 1.0, 1.3)])
+def test_sampler_kernels_folded_into_the_persistent_kernel(t, p, pen, monkeypatch):
+    """Inside a graph of several decode iterations the persistent batch-1 kernel also does the work of the next
+    sampling step's first two kernels (per-block maxima of the penalised scores, weights, level-0 histogram).  Same
+    logits, same expf, same fixed-point masses: the generated stream must be identical, token for token, to the one
+    produced with the three sampler kernels kept apart (SLLM_NO_FOLD), at the real vocabulary and on a small model."""
+    for cfg, std, n_new in ((FULL, 0.02, 70), (MID, 0.05, 100)):
+        prompt = prompt_ids(7, 40, cfg.vocab)
+        us = uniforms(9, n_new).astype(np.float64).reshape(-1, 1)
+        opt = SamplingOptions(temperature=t, top_p=p, repetition_penalty=pen)
+        o, eng = make_pair(cfg, seed=0, stddev=std, fp32=False, via_checkpoint=False)
+        got = eng.generate([prompt], n_new, opt, draws=us, eos=cfg.vocab + 1)[0]
+        monkeypatch.setenv("SLLM_NO_FOLD", "1")
+        _, plain = make_pair(cfg, seed=0, stddev=std, fp32=False, via_checkpoint=False)
+        monkeypatch.delenv("SLLM_NO_FOLD")
+        want = plain.generate([prompt], n_new, opt, draws=us, eos=cfg.vocab + 1)[0]
+        assert got.size == prompt.size + n_new
+        assert np.array_equal(got, want), (cfg.vocab, int(np.argmax(got != want)))
