@@ -42,7 +42,10 @@ LABELS = {
     (422, 424): "hidden-unit gather                         (hand-off 5)",
     (424, 425): "down-projection rows, residual, publish",
     (425, 430): "final x gather + 1/rms",
-    (430, 432): "tied head: vocabulary rows streamed through shared memory",
+    (430, 431): "tied head: vocabulary rows streamed through shared memory",
+    (431, 432): "folded sampler kernels: penalised maxima, hand-off, weights, level-0 histogram",
+    (430, 432): "tied head (no folded sampler work in this launch)",
+    (432, 320): "kernel boundary -> k_samp_pick",
     (432, 300): "kernel boundary -> k_samp_max",
     (300, 310): "k_samp_max -> k_samp_hist",
     (320, 322): "k_samp_pick: weights + level-0 histogram into the block, scan",
