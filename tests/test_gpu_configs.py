@@ -25,6 +25,7 @@ pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
 TOL_F32 = 2e-5
 EOS = 32762
+EOS_NEVER = 1 << 30
 # a model that only carries the sampler: the vocabulary is what matters
 VOCAB_ONLY = Config(vocab=32768, context=128, layers=1, d_model=64, heads=1, ffn=64)
 
@@ -263,3 +264,28 @@ def test_config5_full_depth():
     assert worst <= TOL_BF16
     assert all(m <= 2.5 * e for _, _, m, e in wide), wide
     assert len(flips) <= 4 and len(wide) <= 2, (flips, wide)
+
+
+def test_batch1_decode_to_the_end_of_the_context():
+    """The persistent batch-1 kernel over the last pages of a 2048-position context (31 and 32 KV pages: the most key
+    ranges per head and three pages per range, a page boundary crossed at position 1984): 100.3M model, bf16, prompt of
+    1 975 ids, teacher-forced decode to position 2047, logits against the oracle at every step; then sampling once more
+    fills the context (finished flag 2) and the loop stops there."""
+    cfg = FULL
+    n_prompt, total = 1975, cfg.context
+    ids = prompt_ids(12, total)
+    o, eng = make_pair(cfg, seed=0, stddev=0.02, fp32=False)
+    ref = o.forward(ids, 1, total, row_from=n_prompt - 1)[0]
+    eng.prefill([ids[:n_prompt]])
+    opt = SamplingOptions(temperature=0.0, repetition_penalty=1.0)
+    worst = rel_err(eng.step_logits(0), ref[0])
+    for t in range(n_prompt, total):
+        eng.sample(opt, eos=EOS_NEVER)
+        eng.force_token(0, int(ids[t]))
+        eng.decode_step()
+        worst = max(worst, rel_err(eng.step_logits(0), ref[t - n_prompt + 1]))
+    print(f"batch-1 decode at positions {n_prompt}..{total - 1}: worst logits rel err {worst:.2e}")
+    assert worst <= TOL_BF16
+    assert np.array_equal(eng.tokens(0), ids)
+    eng.decode_loop(5, opt, None, eos=EOS_NEVER)                 # one more token fits; then the slot is full
+    assert eng.tokens(0).size == total + 1 and eng.finished(1)[0] == 2
