@@ -110,9 +110,21 @@ __device__ __forceinline__ void tl_stamp_here(unsigned int id) {
 }
 #define SLLM_TL(id) tl_stamp(id)
 #define SLLM_TL_HERE(id) tl_stamp_here(id)
+// Stamps without a round trip per stamp: thread 0 of the chosen blocks reserves a run of entries once per launch
+// (PS_TL_INIT), then every stamp (PS_TL) is two plain stores.
+#ifndef SLLM_TL_BLOCKS            /* blocks whose thread 0 stamps: 0 only, or (debugging skew between blocks) 0, 37 and the last */
+#define SLLM_TL_BLOCKS 1
+#endif
+#define PS_TL_INIT(n) unsigned int ps_tl_i = 0, ps_tl_end = 0, ps_tl_tag = 0; \
+    if (threadIdx.x == 0 && (blockIdx.x == 0 || (SLLM_TL_BLOCKS > 1 && (blockIdx.x == 37 || blockIdx.x == gridDim.x - 1)))) { \
+        ps_tl_i = atomicAdd(&g_tl_n, (unsigned int)(n)); ps_tl_end = ps_tl_i + (n); ps_tl_tag = blockIdx.x * 10000u; }
+#define PS_TL(id) do { if (ps_tl_i < ps_tl_end && ps_tl_end <= (1u << 15)) { unsigned long long t_; \
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_tl_buf[2 * ps_tl_i] = (id) + ps_tl_tag; g_tl_buf[2 * ps_tl_i + 1] = t_; ++ps_tl_i; } } while (0)
 #else
 #define SLLM_TL(id)
 #define SLLM_TL_HERE(id)
+#define PS_TL_INIT(n)
+#define PS_TL(id)
 #endif
 
 // ---- device-side view of the model and of the running sequences ----------------------------

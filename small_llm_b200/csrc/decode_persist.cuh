@@ -22,7 +22,8 @@
 //     waits (bounded) for its own copies in flight and returns; the others run into the same limit.
 //
 // Measured and dropped: requesting every polled word three times 0.15 us apart (slower: 354 against 329 us per token
-// on the same GPU), sleeping 50-300 ns between two polls of a word (284 -> 364-383 us), splitting a down-projection row over several warps (two more block barriers cost more than the
+// on the same GPU), sleeping 50-300 ns between two polls of a word (284 -> 364-383 us), letting the blocks without an attention role sleep
+// 0.2-2.5 us before they poll for the partials (262.5 -> 258.2 us at best, 270.5 at worst), splitting a down-projection row over several warps (two more block barriers cost more than the
 // shorter sums saved).
 //
 // Buffers are reused by every layer.  That is safe because the hand-offs of x and of the hidden units are
@@ -253,22 +254,6 @@ __device__ __forceinline__ void ps_part(int n, int parts, int i, int& b, int& e)
     b = (int)((long long)n * i / parts);
     e = (int)((long long)n * (i + 1) / parts);
 }
-
-// Timeline stamps of debug builds (-DSLLM_TIMELINE) without a round trip per stamp: block 0 reserves a run of entries
-// once, then every stamp is two plain stores.
-#ifdef SLLM_TIMELINE
-#ifndef SLLM_TL_BLOCKS            /* blocks whose thread 0 stamps: 0 only, or (debugging skew between blocks) 0, 37 and the last */
-#define SLLM_TL_BLOCKS 1
-#endif
-#define PS_TL_INIT(n) unsigned int ps_tl_i = 0, ps_tl_end = 0, ps_tl_tag = 0; \
-    if (threadIdx.x == 0 && (blockIdx.x == 0 || (SLLM_TL_BLOCKS > 1 && (blockIdx.x == 37 || blockIdx.x == gridDim.x - 1)))) { \
-        ps_tl_i = atomicAdd(&g_tl_n, (unsigned int)(n)); ps_tl_end = ps_tl_i + (n); ps_tl_tag = blockIdx.x * 10000u; }
-#define PS_TL(id) do { if (ps_tl_i < ps_tl_end && ps_tl_end <= (1u << 15)) { unsigned long long t_; \
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_tl_buf[2 * ps_tl_i] = (id) + ps_tl_tag; g_tl_buf[2 * ps_tl_i + 1] = t_; ++ps_tl_i; } } while (0)
-#else
-#define PS_TL_INIT(n)
-#define PS_TL(id)
-#endif
 
 enum { PS_B_QKV = 0, PS_B_O = 1, PS_B_GU = 2, PS_B_D = 3, PS_B_KV = 4, PS_B_HEAD = 5, PS_N_BARS = 5 + kPsMaxHeadStages };
 

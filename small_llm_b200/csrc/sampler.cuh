@@ -508,10 +508,11 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
 
     const int slot = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int V = a.V;
+    PS_TL_INIT(16);
     pdl_launch_dependents();
     pdl_wait();
 
-    SLLM_TL(320);
+    PS_TL(320);
     // Everything the sampling path reads from global memory is requested up front, ahead of the maximum's reduction:
     // the first trip of the weights and this thread's share of the level-0 histogram (which is cleared for the
     // next step; a finished slot's histogram is empty and its weights are not used).
@@ -548,6 +549,7 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
             }
         }
     }
+    PS_TL(3201);
     // the slot's maximum (first index among equals) from the per-block maxima
     if (tid < 32) {
         float bv = pv[0]; int bi = pi[0];
@@ -558,6 +560,7 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
         if (tid == 0) { s_val = bv; s_idx = bi; }
     }
     __syncthreads();
+    PS_TL(3202);
     const float mx = s_val; const int arg = s_idx;
     int token = -1;
     if (!fin) {
@@ -568,19 +571,19 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
         } else {
             l0_scan(l0, sc);                                   // ends with a block barrier: w is complete too
             const unsigned long long total = sc.tot_m;
-            SLLM_TL(322);
+            PS_TL(322);
             // ---- top-p: first prefix whose mass reaches top_p of the total -----------------------
             unsigned long long t1 = (unsigned long long)ceil((double)a.top_p * (double)total);
             if (t1 > total) t1 = total + 1;                    // unreachable: everything is kept
             const Loc cut = locate(w, V, t1, l0, h1, sc, cs);
             const unsigned long long kept_mass = cut.mass_incl;
             const unsigned int kept = cut.cnt_incl;
-            SLLM_TL(323);
+            PS_TL(323);
             // ---- the draw -------------------------------------------------------------------------
             unsigned long long t2 = (unsigned long long)ceil(u * (double)kept_mass);
             if (t2 > kept_mass) t2 = kept_mass;
             const Loc hit = locate(w, V, t2, l0, h1, sc, cs);
-            SLLM_TL(324);
+            PS_TL(324);
             const Loc& use = (hit.found && hit.cnt_incl <= kept) ? hit : cut;    // else: the last kept candidate
             if (use.found) {
                 token = use.have_id ? use.id : nth_with_key(w, V, use.key, use.r, s_scan, &s_out);
@@ -602,7 +605,7 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
                 __syncthreads();
                 token = nth_with_key(w, V, kmin, t, s_scan, &s_out);
             }
-            SLLM_TL(325);
+            PS_TL(325);
             if (tid == 0 && (!a.seeded || kept >= 2)) a.st.draw_idx[slot] += 1;
         }
     }
@@ -626,7 +629,7 @@ __global__ void __launch_bounds__(kSampThreads) k_samp_pick(const SampleArgs a) 
         a.next_tok_pos[slot] = p;
         a.next_tok_slot[slot] = slot;
     }
-    SLLM_TL(321);
+    PS_TL(321);
 }
 
 }  // namespace sllm

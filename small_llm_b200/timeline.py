@@ -48,7 +48,9 @@ LABELS = {
     (432, 320): "kernel boundary -> k_samp_pick",
     (432, 300): "kernel boundary -> k_samp_max",
     (300, 310): "k_samp_max -> k_samp_hist",
-    (320, 322): "k_samp_pick: weights + level-0 histogram into the block, scan",
+    (320, 3201): "k_samp_pick: weights + level-0 histogram requested and stored",
+    (3201, 3202): "k_samp_pick: block barrier, the slot's maximum",
+    (3202, 322): "k_samp_pick: scan of the level-0 histogram",
     (322, 323): "k_samp_pick: top-p cut",
     (323, 324): "k_samp_pick: the draw",
     (324, 325): "k_samp_pick: token",
