@@ -124,8 +124,8 @@ def test_string_entry_points_with_a_tokenizer_file(tmp_path):
     subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "facade_text_gpu.cpp"),
                     "-o", exe, "-L", libdir, "-lsllm_b200", f"-Wl,-rpath,{libdir}"], check=True)
     r = subprocess.run([exe, ckpt, tokf, res, str(cfg.vocab), str(cfg.context), str(cfg.layers), str(cfg.d_model), str(cfg.heads),
-                        str(cfg.ffn)], capture_output=True, text=True)
-    assert r.returncode == 0, r.stdout + r.stderr
+                        str(cfg.ffn)], capture_output=True)          # bytes: random weights generate arbitrary byte strings
+    assert r.returncode == 0, r.stdout[-500:] + r.stderr[-500:]
     with open(res, "rb") as f:
         ids = _read(f, np.uint32)
         n = int(np.frombuffer(f.read(8), dtype=np.uint64)[0]); text_out = f.read(n)
@@ -139,4 +139,4 @@ def test_string_entry_points_with_a_tokenizer_file(tmp_path):
     assert chat_ids[0] == 507 and list(chat_ids[-2:]) == [509, 508] and decode(chat_ids[1:-2]) == question
     ref = o.generate(chat_ids, 24, 0.8, 0.9, 1.2, eos=eos, stop=509, seed=4321)
     assert chat_out == decode(ref)
-    assert text_out.decode() in r.stdout                         # generateTokens prints what it returns (src/inference.cpp:167-169)
+    assert text_out in r.stdout                                  # generateTokens prints what it returns (src/inference.cpp:167-169)
