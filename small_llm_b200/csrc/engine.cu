@@ -141,6 +141,8 @@ struct sllm_engine {
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
     int tune_tc_split = 0;             // SLLM_TC_SPLIT: tuning aid, forces the split-K cluster size of the projections
+    int tune_no_wide_epi = 0;          // SLLM_NO_WIDE_EPI: wide projection tiles keep the thread-per-row epilogue (comparison aid)
+    int tune_no_persistent_tc = 0;     // SLLM_NO_PERSISTENT_TC: the wide projections run one tile per block (comparison aid)
     int tune_stream_splits = 0;        // SLLM_STREAM_SPLITS: tuning aid, overrides the split count of the streaming kernel
     unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
     float* samp_w = nullptr; float* samp_pmax_val = nullptr; int* samp_pmax_idx = nullptr;
@@ -389,13 +391,20 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, T
     if (e->tune_tc_split > 0) split = std::min({e->tune_tc_split, kTcMaxSplit, nkb});
     if (tc_smem_bytes(BN, 2, split) > e->max_dyn_smem) split = 1;
     const int kb_per_block = (nkb + split - 1) / split;
-    const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split)) / tc_stage_bytes(BN));
+    // wide tiles without split-K: the transposing epilogue (16-byte accesses need every row count to be a multiple of 4)
+    const bool wide = BN >= 128 && split == 1 && a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
+    a.wide_epi = wide ? 1 : 0;
+    const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split, wide)) / tc_stage_bytes(BN));
     a.split = split;
     const int cap = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10));   // beyond this, measured slower (less room for the next kernel's blocks)
     a.stages = std::max(1, std::min({cap, fit, kb_per_block}));
-    const dim3 grid((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN, split);
+    // more than one wave of tiles: one block per SM walks its tiles with two accumulators (see TcArgs)
+    a.n_tiles = tiles;
+    a.persistent = (split == 1 && 2 * BN <= 512 && tiles > e->sm_count && !e->tune_no_persistent_tc) ? 1 : 0;
+    const dim3 grid = a.persistent ? dim3(std::min(tiles, e->sm_count))
+                                   : dim3((a.R + kTcBM - 1) / kTcBM, (a.n_tok + BN - 1) / BN, split);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid; cfg.blockDim = dim3(tc_threads<BN>()); cfg.dynamicSmemBytes = tc_smem_bytes(BN, a.stages, split); cfg.stream = e->stream;
+    cfg.gridDim = grid; cfg.blockDim = dim3(tc_threads<BN>()); cfg.dynamicSmemBytes = tc_smem_bytes(BN, a.stages, split, wide); cfg.stream = e->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
     if (split > 1) {
@@ -1175,6 +1184,8 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     }
     if (const char* v = std::getenv("SLLM_TC_MIN_TOKENS")) e->tc_min_tokens = std::max(1, std::atoi(v));   // tuning aid
     if (const char* v = std::getenv("SLLM_TC_SPLIT")) e->tune_tc_split = std::max(0, std::atoi(v));
+    if (std::getenv("SLLM_NO_PERSISTENT_TC")) e->tune_no_persistent_tc = 1;
+    if (std::getenv("SLLM_NO_WIDE_EPI")) e->tune_no_wide_epi = 1;
     if (const char* v = std::getenv("SLLM_STREAM_SPLITS")) e->tune_stream_splits = std::min(std::max(0, std::atoi(v)), 8);
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);

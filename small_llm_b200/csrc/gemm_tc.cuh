@@ -55,6 +55,17 @@ struct TcArgs {
     // tile's weight bytes over several SMs, each of which can only take in ~65 GB/s.
     int stages;                     // pipeline stages of this launch (<= kTcMaxStages)
     int split;                      // blocks per cluster (1 = no cluster)
+    // More tiles than the GPU holds blocks (prefill): grid x = resident blocks, block b takes tiles b, b + grid x, ...
+    // with two accumulators in tensor memory, so that the epilogue of one tile (loads and stores scattered by token,
+    // longer than the main loop) runs while the tensor cores work on the next.  Otherwise one tile per block,
+    // taken from the block index.
+    int persistent;
+    int n_tiles;                    // weight row tiles x token tiles
+    // Wide token tiles (16 epilogue warps, no split-K, every row count a multiple of 4): the four warps that share a
+    // column group transpose each 16-column chunk of the accumulator through shared memory, after which a lane holds
+    // four consecutive output rows of one token and loads / stores 16 bytes at a time -- a tenth of the address
+    // arithmetic and memory instructions of the thread-per-row epilogue, which is bound by instruction issue.
+    int wide_epi;
 };
 
 // Sums v[j] over the 32 lanes for every j at once: afterwards lane j holds the sum of all lanes' v[j] (31 shuffles,
@@ -135,12 +146,16 @@ template <int CW> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t
 
 // Shared memory of one block: [1 KB alignment slack][stages x (weight tile | token tile)][barriers, TMEM slot: 512 B]
 // [token metadata: per epilogue warp its columns' positions, pages and 1/rms: 12 x BN words in all][split > 1: (split - 1) accumulators of 128 x BN floats handed over
-// by the peers]
+// by the peers | wide epilogue: the column groups' transposition buffers]
 constexpr size_t tc_stage_bytes(int bn) { return (size_t)kTcBM * kTcBK * 2 + (size_t)bn * kTcBK * 2; }
-constexpr size_t tc_fixed_bytes(int bn, int split) {
-    return 1024 + 512 + (size_t)12 * bn * sizeof(int) + (size_t)(split - 1) * kTcBM * bn * sizeof(float);
+constexpr size_t kTcWideStageBytes = (size_t)4 * 2 * 16 * kTcBM * sizeof(float);   // wide epilogue: 4 column groups x 2 buffers x [16 columns][128 rows]
+constexpr size_t tc_fixed_bytes(int bn, int split, bool wide = false) {
+    return 1024 + 512 + (size_t)12 * bn * sizeof(int) +
+           (wide ? kTcWideStageBytes : (size_t)(split - 1) * kTcBM * bn * sizeof(float));
 }
-constexpr size_t tc_smem_bytes(int bn, int stages, int split) { return tc_fixed_bytes(bn, split) + (size_t)stages * tc_stage_bytes(bn); }
+constexpr size_t tc_smem_bytes(int bn, int stages, int split, bool wide = false) {
+    return tc_fixed_bytes(bn, split, wide) + (size_t)stages * tc_stage_bytes(bn);
+}
 
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -156,6 +171,19 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+// barrier `id` over 128 threads (the four warps of a column group) that also ANDs a flag over them
+__device__ __forceinline__ bool group_sync_and(int id, bool flag) {
+    uint32_t out;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, %2, 128, q;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(out) : "r"((uint32_t)flag), "r"(id) : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 template <int BN, int MODE>
 __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_constant__ CUtensorMap map_w,
                                                         const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
@@ -165,15 +193,20 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[16], empty[16], done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcMaxStages + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);   // full[16], empty[16], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcMaxStages + 4);
     int* tok_meta = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);   // [epilogue warps][pos | page of the warp's columns]
     float* tok_rs = reinterpret_cast<float*>(tok_meta + 8 * BN);            // [epilogue warps][its columns]: 1/rms of the warp's tokens
     float* handover = tok_rs + 4 * BN;                                      // [split - 1][BN][128] in block 0 of the cluster
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcMaxStages), done_bar = smem_u32(bars + 2 * kTcMaxStages);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcMaxStages);
+    const uint32_t accf0 = smem_u32(bars + 2 * kTcMaxStages), acce0 = accf0 + 16;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * kTcBM, t0 = blockIdx.y * BN;
+    const int tiles_m = (a.R + kTcBM - 1) / kTcBM;
+    // this block's tiles: first, first + step, ... (one tile unless persistent)
+    const int tile_first = a.persistent ? (int)blockIdx.x : (int)(blockIdx.y * tiles_m + blockIdx.x);
+    const int tile_step = a.persistent ? (int)gridDim.x : a.n_tiles;
+    const uint32_t n_acc = a.persistent ? 2u : 1u;                          // accumulators in tensor memory
     const int split = a.split, ks = blockIdx.z;                             // the cluster spans grid z
     const int nkb_all = (a.K + kTcBK - 1) / kTcBK;
     const int kb_first = (nkb_all * ks) / split;
@@ -181,11 +214,11 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(done_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(accf0 + 8 * b, 1); mbar_init(acce0 + 8 * b, tc_epi_warps<BN>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(n_acc * BN));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     tc_fence_before();
@@ -195,10 +228,11 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
 
     SLLM_TL(500 + MODE * 10);
     pdl_launch_dependents();
-    // The weight tiles do not depend on the predecessor kernel: the first STAGES of them are requested before
-    // the dependency wait (the barrier already expects the bytes of both operands of its stage).
+    // The weight tiles do not depend on the predecessor kernel: the first STAGES of them (of the block's first tile)
+    // are requested before the dependency wait (the barrier already expects the bytes of both operands of its stage).
     const int pre = nkb < STAGES ? nkb : STAGES;
     if (warp == 0 && lane == 0) {
+        const int m0 = (tile_first % tiles_m) * kTcBM;
         for (int kb = 0; kb < pre; ++kb) {
             mbar_expect_tx(full0 + 8 * kb, A_BYTES + B_BYTES);
             tma_load_2d(smem_u32(sA + kb * A_BYTES), &map_w, (kb_first + kb) * kTcBK, m0, full0 + 8 * kb);
@@ -213,15 +247,18 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
             // stage index and round kept as counters: the stage count is a launch parameter, and an integer
             // division per K block on this single thread would be on the critical path
             int s = 0; uint32_t round = 0;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                if (kb >= pre) {
-                    ok = mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.status, 11);
-                    if (!ok) break;
-                    mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
-                    tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, (kb_first + kb) * kTcBK, m0, full0 + 8 * s);
+            for (int tile = tile_first; tile < a.n_tiles && ok; tile += tile_step) {
+                const int m0 = (tile % tiles_m) * kTcBM, t0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < nkb && ok; ++kb) {
+                    if (tile != tile_first || kb >= pre) {
+                        ok = mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.status, 11);
+                        if (!ok) break;
+                        mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                        tma_load_2d(smem_u32(sA + s * A_BYTES), &map_w, (kb_first + kb) * kTcBK, m0, full0 + 8 * s);
+                    }
+                    tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, (kb_first + kb) * kTcBK, t0, full0 + 8 * s);
+                    if (++s == STAGES) { s = 0; ++round; }
                 }
-                tma_load_2d(smem_u32(sB + s * B_BYTES), &map_x, (kb_first + kb) * kTcBK, t0, full0 + 8 * s);
-                if (++s == STAGES) { s = 0; ++round; }
             }
         }
         __syncwarp();
@@ -229,21 +266,29 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = tc_idesc(kTcBM, BN);
-            int s = 0; uint32_t round = 0;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                ok = mbar_wait(full0 + 8 * s, round & 1, a.status, 12);
+            int s = 0; uint32_t round = 0, it = 0;
+            for (int tile = tile_first; tile < a.n_tiles && ok; tile += tile_step, ++it) {
+                // the accumulator this tile goes to must have been read out by the epilogue of the tile two before
+                const uint32_t buf = it & (n_acc - 1), use = it / n_acc;
+                ok = mbar_wait(acce0 + 8 * buf, (use - 1) & 1, a.status, 14);
                 if (!ok) break;
                 tc_fence_after();
-                if (kb == 0) SLLM_TL_HERE(502 + MODE * 10);
-                if (kb == nkb - 1) SLLM_TL_HERE(505 + MODE * 10);
-                const uint32_t aaddr = smem_u32(sA + s * A_BYTES), baddr = smem_u32(sB + s * B_BYTES);
+                const uint32_t acc = tmem + buf * BN;
+                for (int kb = 0; kb < nkb && ok; ++kb) {
+                    ok = mbar_wait(full0 + 8 * s, round & 1, a.status, 12);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (kb == 0) SLLM_TL_HERE(502 + MODE * 10);
+                    if (kb == nkb - 1) SLLM_TL_HERE(505 + MODE * 10);
+                    const uint32_t aaddr = smem_u32(sA + s * A_BYTES), baddr = smem_u32(sB + s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < kTcBK / 16; ++k)
-                    tc_mma_bf16(tmem, tc_smem_desc(aaddr + k * 32), tc_smem_desc(baddr + k * 32), idesc, (kb | k) != 0);
-                tc_commit(empty0 + 8 * s);          // the stage may be refilled once these MMAs have read it
-                if (++s == STAGES) { s = 0; ++round; }
+                    for (int k = 0; k < kTcBK / 16; ++k)
+                        tc_mma_bf16(acc, tc_smem_desc(aaddr + k * 32), tc_smem_desc(baddr + k * 32), idesc, (kb | k) != 0);
+                    tc_commit(empty0 + 8 * s);          // the stage may be refilled once these MMAs have read it
+                    if (++s == STAGES) { s = 0; ++round; }
+                }
+                if (ok) tc_commit(accf0 + 8 * buf);     // accumulator complete
             }
-            if (ok) tc_commit(done_bar);            // accumulator complete
         }
         __syncwarp();
         if (split > 1) cluster_sync_all();
@@ -255,169 +300,271 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
         const int ew = warp - 2;
         const int quarter = warp & 3;
         const int cbeg = (ew >> 2) * HALF;
-        const int row = m0 + quarter * 32 + lane;
-        const bool row_ok = row < a.R;
-        const int D = a.m.D, hd = a.m.hd;
-        int which = 0, col = 0, head = 0, d = 0;
-        if (MODE == kModeQKV && row_ok) { which = row / D; col = row - which * D; head = col / hd; d = col - head * hd; }
-        // While the tensor cores work, each epilogue warp fetches the positions and KV pages of its tokens into
-        // its own shared-memory copy, and the operands of its first column chunk that do not depend on the
-        // accumulator (rotation factors, residual values), so that little is left to wait for afterwards.
-        // per token: its position (for the rotation factors) and the row of the KV pool, in units of head_dim
-        // elements, at which head 0's K entry of that position lies
-        int* my_pos = tok_meta + ew * 2 * HALF;
-        uint32_t* my_kvrow = reinterpret_cast<uint32_t*>(my_pos + HALF);
-        if (MODE == kModeQKV) {
-            for (int j = lane; j < HALF; j += 32) {
-                const int tok = t0 + cbeg + j;
-                int pos = 0, page = 0;
-                if (tok < a.n_tok) {
-                    pos = a.pass.tok_pos[tok];
-                    page = a.kv.block_table[(size_t)a.pass.tok_slot[tok] * a.kv.pages_per_seq + pos / kPage];
-                }
-                my_pos[j] = pos;
-                my_kvrow[j] = (uint32_t)((((unsigned long long)a.layer * a.kv.n_pages + page) * 2 * a.m.H) * kPage + pos % kPage);
-            }
-            __syncwarp();
-        }
-        // this lane's constant part of the addresses it loads from and stores to
-        float* const x_lane = a.out + row;                       // Residual / Head: [tok][R] fp32
-        __nv_bfloat16* const xn_lane = a.xn_out + row;
-        float* const q_lane = a.out + col;
-        __nv_bfloat16* const kv_lane = reinterpret_cast<__nv_bfloat16*>(a.kv.pool) + d;
-        const uint32_t kv_lane_row = (uint32_t)(((which > 0 ? which - 1 : 0) * a.m.H + head) * kPage);
-        float2 cs[MODE == kModeQKV ? CW : 1];
-        float xv[MODE == kModeResidual ? CW : 1];
-        const bool scaled = (MODE == kModeQKV || MODE == kModeGateUp) && a.ss_in != nullptr;
-        const float gnext = (MODE == kModeResidual && a.gain_next && row_ok) ? a.gain_next[row] : 0.f;
-        // consumers of a folded norm: 1/rms of each of the warp's tokens, from the producer's partial sums of squares
-        float* my_rs = tok_rs + ew * HALF;
-        if (MODE == kModeQKV || MODE == kModeGateUp) {
-            for (int j = lane; j < HALF; j += 32) {
-                const int tok = t0 + cbeg + j;
-                float r = 1.0f;
-                if (scaled && ks == 0 && tok < a.n_tok) {        // n_parts is a multiple of 4: 16-byte loads, 8 in flight per trip
-                    const float4* pp = reinterpret_cast<const float4*>(a.ss_in + (size_t)tok * a.n_parts);
-                    const int n4 = a.n_parts / 4;
-                    float ss = 0.f;
-                    for (int p0 = 0; p0 < n4; p0 += 8) {
-                        float4 q[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) q[i] = p0 + i < n4 ? pp[p0 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) ss += (q[i].x + q[i].y) + (q[i].z + q[i].w);
-                    }
-                    r = 1.0f / sqrtf(ss / (float)a.K + a.eps);
-                }
-                my_rs[j] = r;
-            }
-            __syncwarp();
-        }
-        auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
+        uint32_t it = 0;
+        for (int tile = tile_first; tile < a.n_tiles && ok; tile += tile_step, ++it) {
+            const int mi = tile % tiles_m, m0 = mi * kTcBM, t0 = (tile / tiles_m) * BN;
+            const uint32_t buf = it & (n_acc - 1);
+            const uint32_t acc = tmem + buf * BN;                   // this tile's accumulator
+            const int row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < a.R;
+            const int D = a.m.D, hd = a.m.hd;
+            int which = 0, col = 0, head = 0, d = 0;
+            if (MODE == kModeQKV && row_ok) { which = row / D; col = row - which * D; head = col / hd; d = col - head * hd; }
+            // While the tensor cores work, each epilogue warp fetches the positions and KV pages of its tokens into
+            // its own shared-memory copy, and the operands of its first column chunk that do not depend on the
+            // accumulator (rotation factors, residual values), so that little is left to wait for afterwards.
+            // per token: its position (for the rotation factors) and the row of the KV pool, in units of head_dim
+            // elements, at which head 0's K entry of that position lies
+            int* my_pos = tok_meta + ew * 2 * HALF;
+            uint32_t* my_kvrow = reinterpret_cast<uint32_t*>(my_pos + HALF);
             if (MODE == kModeQKV) {
+                for (int j = lane; j < HALF; j += 32) {
+                    const int tok = t0 + cbeg + j;
+                    int pos = 0, page = 0;
+                    if (tok < a.n_tok) {
+                        pos = a.pass.tok_pos[tok];
+                        page = a.kv.block_table[(size_t)a.pass.tok_slot[tok] * a.kv.pages_per_seq + pos / kPage];
+                    }
+                    my_pos[j] = pos;
+                    my_kvrow[j] = (uint32_t)((((unsigned long long)a.layer * a.kv.n_pages + page) * 2 * a.m.H) * kPage + pos % kPage);
+                }
+                __syncwarp();
+            }
+            // this lane's constant part of the addresses it loads from and stores to
+            float* const x_lane = a.out + row;                       // Residual / Head: [tok][R] fp32
+            __nv_bfloat16* const xn_lane = a.xn_out + row;
+            float* const q_lane = a.out + col;
+            __nv_bfloat16* const kv_lane = reinterpret_cast<__nv_bfloat16*>(a.kv.pool) + d;
+            const uint32_t kv_lane_row = (uint32_t)(((which > 0 ? which - 1 : 0) * a.m.H + head) * kPage);
+            float2 cs[MODE == kModeQKV ? CW : 1];
+            float xv[MODE == kModeResidual ? CW : 1];
+            const bool scaled = (MODE == kModeQKV || MODE == kModeGateUp) && a.ss_in != nullptr;
+            const float gnext = (MODE == kModeResidual && a.gain_next && row_ok) ? a.gain_next[row] : 0.f;
+            // consumers of a folded norm: 1/rms of each of the warp's tokens, from the producer's partial sums of squares
+            float* my_rs = tok_rs + ew * HALF;
+            if (MODE == kModeQKV || MODE == kModeGateUp) {
+                for (int j = lane; j < HALF; j += 32) {
+                    const int tok = t0 + cbeg + j;
+                    float r = 1.0f;
+                    if (scaled && ks == 0 && tok < a.n_tok) {        // n_parts is a multiple of 4: 16-byte loads, 8 in flight per trip
+                        const float4* pp = reinterpret_cast<const float4*>(a.ss_in + (size_t)tok * a.n_parts);
+                        const int n4 = a.n_parts / 4;
+                        float ss = 0.f;
+                        for (int p0 = 0; p0 < n4; p0 += 8) {
+                            float4 q[8];
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) q[i] = p0 + i < n4 ? pp[p0 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) ss += (q[i].x + q[i].y) + (q[i].z + q[i].w);
+                        }
+                        r = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+                    }
+                    my_rs[j] = r;
+                }
+                __syncwarp();
+            }
+            if constexpr (EW == 16) {
+                if (a.wide_epi) {
+                    // ---- wide tiles: transpose through shared memory, four consecutive rows per lane -----------------
+                    const int grp = ew >> 2;
+                    float* const stg = handover + (size_t)grp * 2 * 16 * kTcBM;      // this group's two buffers [16][128]
+                    const int r0 = m0 + 4 * lane;
+                    const bool r_ok = r0 < a.R;                                      // R is a multiple of 4: all four rows or none
+                    int w_which = 0, w_col = 0, w_head = 0, w_d = 0;
+                    if (MODE == kModeQKV && r_ok) { w_which = r0 / D; w_col = r0 - w_which * D; w_head = w_col / hd; w_d = w_col - w_head * hd; }
+                    float4 gn = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (MODE == kModeResidual && a.gain_next && r_ok) gn = *reinterpret_cast<const float4*>(a.gain_next + r0);
+                    const uint32_t kv_head_row = (uint32_t)(((w_which > 0 ? w_which - 1 : 0) * a.m.H + w_head) * kPage);
+                    ok = mbar_wait(accf0 + 8 * buf, (it / n_acc) & 1, a.status, 13);
+                    ok = group_sync_and(1 + grp, ok);                // the four warps go on together or not at all
+                    tc_fence_after();
+                    if (warp == 2 && lane == 0) SLLM_TL_HERE(503 + MODE * 10);
+                    int chunk = 0;
+                    for (int c0 = cbeg; c0 < cbeg + HALF && ok; c0 += 16, ++chunk) {
+                        if (t0 + c0 >= a.n_tok) break;               // uniform over the group
+                        const int cj = c0 + quarter * 4;             // this warp's four columns after the transposition
+                        float4 opnd[4];                              // operands that do not depend on the accumulator
 #pragma unroll
-                for (int j = 0; j < CW; ++j)
-                    cs[j] = (which < 2 && row_ok) ? a.rope[(size_t)my_pos[c - cbeg + j] * (hd / 2) + (d >> 1)] : make_float2(1.f, 0.f);
-            } else if (MODE == kModeResidual) {
+                        for (int i = 0; i < 4; ++i) {
+                            const int tok = t0 + cj + i;
+                            const bool valid = r_ok && tok < a.n_tok;
+                            if (MODE == kModeResidual)
+                                opnd[i] = valid ? *reinterpret_cast<const float4*>(a.out + (size_t)tok * a.R + r0) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            else if (MODE == kModeQKV)
+                                opnd[i] = (valid && w_which < 2)
+                                              ? *reinterpret_cast<const float4*>(a.rope + (size_t)my_pos[cj - cbeg + i] * (hd / 2) + (w_d >> 1))
+                                              : make_float4(1.f, 0.f, 1.f, 0.f);
+                        }
+                        uint32_t v[16];
+                        tc_ld16(acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                        float* const sb = stg + (chunk & 1) * 16 * kTcBM;
 #pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const int tok = t0 + c + j;
-                    xv[j] = (row_ok && tok < a.n_tok) ? x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] : 0.f;
+                        for (int j = 0; j < 16; ++j) sb[j * kTcBM + quarter * 32 + lane] = __uint_as_float(v[j]);
+                        // One barrier per chunk is enough with two buffers: a warp that writes chunk k + 2 has passed
+                        // the barrier of chunk k + 1, which every warp reaches only after its reads of chunk k.
+                        group_sync(1 + grp);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int tok = t0 + cj + i;
+                            if (tok >= a.n_tok) break;               // uniform over the warp
+                            const float4 w = *reinterpret_cast<const float4*>(sb + (quarter * 4 + i) * kTcBM + 4 * lane);
+                            if (MODE == kModeResidual) {
+                                const float4 r = make_float4(opnd[i].x + w.x, opnd[i].y + w.y, opnd[i].z + w.z, opnd[i].w + w.w);
+                                if (r_ok) {
+                                    *reinterpret_cast<float4*>(a.out + (size_t)tok * a.R + r0) = r;
+                                    if (a.gain_next)
+                                        *reinterpret_cast<uint2*>(a.xn_out + (size_t)tok * a.R + r0) =
+                                            make_uint2(pack_bf16x2(r.x * gn.x, r.y * gn.y), pack_bf16x2(r.z * gn.z, r.w * gn.w));
+                                }
+                                if (a.gain_next) {                   // uniform over the grid: the 32-row slices' sums of squares
+                                    float sq = r_ok ? (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w) : 0.f;
+                                    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                                    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                                    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                                    if ((lane & 7) == 0) a.ss_out[(size_t)tok * a.n_parts + mi * 4 + (lane >> 3)] = sq;
+                                }
+                            } else if (MODE == kModeHead) {
+                                if (r_ok) *reinterpret_cast<float4*>(a.out + (size_t)tok * a.R + r0) = w;
+                            } else if (MODE == kModeGateUp) {        // rows: gate, up, gate, up of two hidden units
+                                const float rs = my_rs[cj - cbeg + i];
+                                const float g0 = w.x * rs, u0 = w.y * rs, g1 = w.z * rs, u1 = w.w * rs;
+                                const float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                                const float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                                if (r_ok) *reinterpret_cast<uint32_t*>(a.out_bf16 + (size_t)tok * (a.R / 2) + (r0 >> 1)) = pack_bf16x2(h0, h1);
+                            } else {                                 // QKV: two RoPE pairs per lane
+                                const float rs = my_rs[cj - cbeg + i];
+                                float4 r = make_float4(w.x * rs, w.y * rs, w.z * rs, w.w * rs);
+                                if (w_which < 2) {
+                                    const float4 cs4 = opnd[i];      // cos, sin of the two pairs
+                                    r = make_float4(r.x * cs4.x - r.y * cs4.y, r.x * cs4.y + r.y * cs4.x,
+                                                    r.z * cs4.z - r.w * cs4.w, r.z * cs4.w + r.w * cs4.z);
+                                }
+                                if (r_ok) {
+                                    if (w_which == 0) *reinterpret_cast<float4*>(a.out + (size_t)tok * D + w_col) = r;
+                                    else
+                                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.kv.pool) +
+                                                                  (size_t)(my_kvrow[cj - cbeg + i] + kv_head_row) * (uint32_t)hd + w_d) =
+                                            make_uint2(pack_bf16x2(r.x, r.y), pack_bf16x2(r.z, r.w));
+                                }
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * buf) : "memory");
+                    continue;
                 }
             }
-        };
-        if (ks == 0 && t0 + cbeg < a.n_tok) fetch(cbeg);
-        ok = mbar_wait(done_bar, 0, a.status, 13);
-        ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
-        tc_fence_after();
-        if (warp == 2 && lane == 0) SLLM_TL_HERE(503 + MODE * 10);
-        if (split > 1) {
-            if (ks > 0 && ok) {                                  // hand this block's accumulator to block 0: [peer][column][row]
-                const uint32_t base = cluster_map(smem_u32(handover), 0);
-                for (int c0 = cbeg; c0 < cbeg + HALF; c0 += CW) {
-                    if (t0 + c0 >= a.n_tok) break;
-                    uint32_t v[CW];
-                    tc_ld<CW>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-#pragma unroll
+            auto fetch = [&](int c) {                                // operands of columns c .. c + CW - 1
+                if (MODE == kModeQKV) {
+    #pragma unroll
                     for (int j = 0; j < CW; ++j)
-                        st_cluster_f32(base + 4u * (uint32_t)(((ks - 1) * BN + c0 + j) * kTcBM + quarter * 32 + lane), __uint_as_float(v[j]));
-                }
-            }
-            cluster_sync_all();                                  // every thread of every block of the cluster, exactly once
-        }
-        for (int c0 = cbeg; c0 < cbeg + HALF && ok && ks == 0; c0 += CW) {
-            if (t0 + c0 >= a.n_tok) break;                       // uniform over the warp
-            const bool more = c0 + CW < cbeg + HALF && t0 + c0 + CW < a.n_tok;
-            uint32_t v[CW];
-            tc_ld<CW>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-            for (int p = 0; p + 1 < split; ++p) {                // peers' shares, in rank order
-#pragma unroll
-                for (int j = 0; j < CW; ++j)
-                    v[j] = __float_as_uint(__uint_as_float(v[j]) + handover[((p * BN + c0 + j) * kTcBM) + quarter * 32 + lane]);
-            }
-            if (MODE == kModeResidual) {
-                float r[CW];
-#pragma unroll
-                for (int j = 0; j < CW; ++j) r[j] = xv[j] + __uint_as_float(v[j]);
-                if (more) fetch(c0 + CW);
-#pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const int tok = t0 + c0 + j;
-                    if (row_ok && tok < a.n_tok) {
-                        x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = r[j];
-                        if (a.gain_next) xn_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = __float2bfloat16_rn(r[j] * gnext);
+                        cs[j] = (which < 2 && row_ok) ? a.rope[(size_t)my_pos[c - cbeg + j] * (hd / 2) + (d >> 1)] : make_float2(1.f, 0.f);
+                } else if (MODE == kModeResidual) {
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        const int tok = t0 + c + j;
+                        xv[j] = (row_ok && tok < a.n_tok) ? x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] : 0.f;
                     }
                 }
-                if (a.gain_next) {                               // uniform over the grid
-                    float sq[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) sq[j] = (j < CW && row_ok && t0 + c0 + j < a.n_tok) ? r[j < CW ? j : 0] * r[j < CW ? j : 0] : 0.f;
-                    const float col = warp_column_sums(sq, lane);
-                    const int tok = t0 + c0 + lane;
-                    if (lane < CW && tok < a.n_tok) a.ss_out[(size_t)tok * a.n_parts + blockIdx.x * 4 + quarter] = col;
+            };
+            if (ks == 0 && t0 + cbeg < a.n_tok) fetch(cbeg);
+            ok = mbar_wait(accf0 + 8 * buf, (it / n_acc) & 1, a.status, 13);
+            ok = __all_sync(0xffffffffu, ok);                        // the TMEM loads below need the whole warp
+            tc_fence_after();
+            if (warp == 2 && lane == 0) SLLM_TL_HERE(503 + MODE * 10);
+            if (split > 1) {
+                if (ks > 0 && ok) {                                  // hand this block's accumulator to block 0: [peer][column][row]
+                    const uint32_t base = cluster_map(smem_u32(handover), 0);
+                    for (int c0 = cbeg; c0 < cbeg + HALF; c0 += CW) {
+                        if (t0 + c0 >= a.n_tok) break;
+                        uint32_t v[CW];
+                        tc_ld<CW>(acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+    #pragma unroll
+                        for (int j = 0; j < CW; ++j)
+                            st_cluster_f32(base + 4u * (uint32_t)(((ks - 1) * BN + c0 + j) * kTcBM + quarter * 32 + lane), __uint_as_float(v[j]));
+                    }
                 }
-            } else if (MODE == kModeHead) {
-#pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const int tok = t0 + c0 + j;
-                    if (row_ok && tok < a.n_tok) x_lane[(size_t)tok * a.R] = __uint_as_float(v[j]);
+                cluster_sync_all();                                  // every thread of every block of the cluster, exactly once
+            }
+            for (int c0 = cbeg; c0 < cbeg + HALF && ok && ks == 0; c0 += CW) {
+                if (t0 + c0 >= a.n_tok) break;                       // uniform over the warp
+                const bool more = c0 + CW < cbeg + HALF && t0 + c0 + CW < a.n_tok;
+                uint32_t v[CW];
+                tc_ld<CW>(acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                for (int p = 0; p + 1 < split; ++p) {                // peers' shares, in rank order
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + handover[((p * BN + c0 + j) * kTcBM) + quarter * 32 + lane]);
                 }
-            } else if (MODE == kModeGateUp) {
-                // (gate, up) of a hidden unit sit in adjacent lanes.  Two columns per step: the even lane finishes
-                // column j (its own gate, the neighbour's up), the odd lane column j + 1 (the neighbour's gate, its
-                // own up), so one exchange and one SiLU serve two tokens and every lane's result is stored
-                const bool odd = (row & 1) != 0;
-                __nv_bfloat16* const h_lane = a.out_bf16 + (row >> 1);
-                const uint32_t h_stride = (uint32_t)(a.R / 2);
-#pragma unroll
-                for (int j = 0; j < CW; j += 2) {
-                    const float a0 = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
-                    const float a1 = __uint_as_float(v[j + 1]) * my_rs[c0 - cbeg + j + 1];
-                    const float recv = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
-                    const float g = odd ? recv : a0, u = odd ? a1 : recv;
-                    const float hval = __fdividef(g, 1.0f + __expf(-g)) * u;
-                    const int tok = t0 + c0 + j + (odd ? 1 : 0);
-                    if (row_ok && tok < a.n_tok) h_lane[(size_t)((uint32_t)tok * h_stride)] = __float2bfloat16_rn(hval);
-                }
-            } else {
-                // RoPE pairs sit in adjacent lanes
-                float r[CW];
-#pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const float acc = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
-                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
-                    r[j] = acc;
-                    if (which < 2) r[j] = (row & 1) ? (other * cs[j].y + acc * cs[j].x) : (acc * cs[j].x - other * cs[j].y);
-                }
-                if (more) fetch(c0 + CW);
-#pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const int tok = t0 + c0 + j;
-                    if (!row_ok || tok >= a.n_tok) continue;
-                    if (which == 0) q_lane[(uint32_t)tok * (uint32_t)D] = r[j];
-                    else kv_lane[(size_t)(my_kvrow[c0 - cbeg + j] + kv_lane_row) * (uint32_t)hd] = __float2bfloat16_rn(r[j]);
+                if (MODE == kModeResidual) {
+                    float r[CW];
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) r[j] = xv[j] + __uint_as_float(v[j]);
+                    if (more) fetch(c0 + CW);
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        const int tok = t0 + c0 + j;
+                        if (row_ok && tok < a.n_tok) {
+                            x_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = r[j];
+                            if (a.gain_next) xn_lane[(size_t)((uint32_t)tok * (uint32_t)a.R)] = __float2bfloat16_rn(r[j] * gnext);
+                        }
+                    }
+                    if (a.gain_next) {                               // uniform over the grid
+                        float sq[32];
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j) sq[j] = (j < CW && row_ok && t0 + c0 + j < a.n_tok) ? r[j < CW ? j : 0] * r[j < CW ? j : 0] : 0.f;
+                        const float col = warp_column_sums(sq, lane);
+                        const int tok = t0 + c0 + lane;
+                        if (lane < CW && tok < a.n_tok) a.ss_out[(size_t)tok * a.n_parts + mi * 4 + quarter] = col;
+                    }
+                } else if (MODE == kModeHead) {
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        const int tok = t0 + c0 + j;
+                        if (row_ok && tok < a.n_tok) x_lane[(size_t)tok * a.R] = __uint_as_float(v[j]);
+                    }
+                } else if (MODE == kModeGateUp) {
+                    // (gate, up) of a hidden unit sit in adjacent lanes.  Two columns per step: the even lane finishes
+                    // column j (its own gate, the neighbour's up), the odd lane column j + 1 (the neighbour's gate, its
+                    // own up), so one exchange and one SiLU serve two tokens and every lane's result is stored
+                    const bool odd = (row & 1) != 0;
+                    __nv_bfloat16* const h_lane = a.out_bf16 + (row >> 1);
+                    const uint32_t h_stride = (uint32_t)(a.R / 2);
+    #pragma unroll
+                    for (int j = 0; j < CW; j += 2) {
+                        const float a0 = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
+                        const float a1 = __uint_as_float(v[j + 1]) * my_rs[c0 - cbeg + j + 1];
+                        const float recv = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+                        const float g = odd ? recv : a0, u = odd ? a1 : recv;
+                        const float hval = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        const int tok = t0 + c0 + j + (odd ? 1 : 0);
+                        if (row_ok && tok < a.n_tok) h_lane[(size_t)((uint32_t)tok * h_stride)] = __float2bfloat16_rn(hval);
+                    }
+                } else {
+                    // RoPE pairs sit in adjacent lanes
+                    float r[CW];
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        const float mine = __uint_as_float(v[j]) * my_rs[c0 - cbeg + j];
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        r[j] = mine;
+                        if (which < 2) r[j] = (row & 1) ? (other * cs[j].y + mine * cs[j].x) : (mine * cs[j].x - other * cs[j].y);
+                    }
+                    if (more) fetch(c0 + CW);
+    #pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        const int tok = t0 + c0 + j;
+                        if (!row_ok || tok >= a.n_tok) continue;
+                        if (which == 0) q_lane[(uint32_t)tok * (uint32_t)D] = r[j];
+                        else kv_lane[(size_t)(my_kvrow[c0 - cbeg + j] + kv_lane_row) * (uint32_t)hd] = __float2bfloat16_rn(r[j]);
+                    }
                 }
             }
+            // the accumulator has been read out: the tensor cores may overwrite it (tile after next)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * buf) : "memory");
         }
     }
     if (warp == 2 && lane == 0) SLLM_TL_HERE(504 + MODE * 10);
@@ -428,7 +575,7 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(n_acc * BN));
     }
 }
 
