@@ -98,7 +98,8 @@ struct sllm_engine {
     int spare_page = 0;                // never handed out: idle slots write their (ignored) K/V there
 
     // pass buffers
-    int pass_cap = 0;                  // tokens per pass
+    int pass_cap = 0;                  // tokens per pass (size of the pass buffers)
+    int chunk_tokens = 0;              // prompt positions per prefill chunk (<= pass_cap)
     uint32_t* d_tok_id = nullptr; int* d_tok_slot = nullptr; int* d_tok_pos = nullptr;
     uint32_t* d_dec_id = nullptr; int* d_dec_slot = nullptr; int* d_dec_pos = nullptr;   // decode pass (written by the sampler)
     int* d_attn_order = nullptr;       // decode pass: slots by descending length, the attention grid's block order
@@ -1039,6 +1040,26 @@ int check_status(sllm_engine* e) {
     return SLLM_OK;
 }
 
+// Prompt positions per prefill chunk when the caller leaves the choice to the engine.  A chunk's four projections run
+// as 128 x 256 tiles, one block per SM walking its tiles, so a projection takes ceil(tiles / SMs) rounds whatever the
+// fill of the last round: 8192 positions of the 100.3M model are 480 / 160 / 864 / 160 tiles = 4 / 2 / 6 / 2 rounds
+// on 148 SMs, 7424 positions are 435 / 145 / 783 / 145 tiles = 3 / 1 / 6 / 1 rounds.  Picks the multiple of 256 in
+// the upper half of the pass buffers with the fewest modelled microseconds per position (a round costs a tile's time:
+// a fixed part for the epilogue -- smaller for the SiLU epilogue, which stores half as much -- plus the K blocks).
+int pick_chunk_tokens(int cap, int D, int F, int sms) {
+    if (cap < 2048) return cap;
+    double best = 0.0; int best_t = cap;
+    for (int t = cap - cap % 256; t >= cap / 2; t -= 256) {
+        const int tn = (t + 255) / 256;
+        auto rounds = [&](int R) { return (double)((((R + kTcBM - 1) / kTcBM) * tn + sms - 1) / sms); };
+        const double kd = 0.5 * ((D + kTcBK - 1) / kTcBK), kf = 0.5 * ((F + kTcBK - 1) / kTcBK);
+        const double us = rounds(3 * D) * (6.0 + kd) + rounds(D) * (6.0 + kd) + rounds(2 * F) * (2.5 + kd) + rounds(D) * (6.0 + kf);
+        const double per_pos = us / t;
+        if (best == 0.0 || per_pos < best * 0.995) { best = per_pos; best_t = t; }   // ties go to the larger chunk
+    }
+    return best_t;
+}
+
 // Runs every prompt position through the model in chunks.  want_all: logits of every position go
 // to host_logits [sum(lens)][V]; otherwise the last position of each slot goes to step_logits.
 // pos0s: first position of each sequence's ids (tokens appended behind what the slot's KV cache already holds).
@@ -1094,7 +1115,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
     };
     for (uint32_t s = 0; s < n_seq; ++s) {
         for (uint32_t i = 0; i < lens[s]; ++i) {
-            if ((int)c_id.size() == e->pass_cap) { int rc = flush(); if (rc) return rc; }
+            if ((int)c_id.size() == e->chunk_tokens) { int rc = flush(); if (rc) return rc; }
             const int slot = slot_ids ? slot_ids[s] : (int)s;
             const int pos = (pos0s ? pos0s[s] : 0) + (int)i;
             if (host_logits || h_targets || i + 1 == lens[s]) { c_row.push_back((int)c_id.size()); c_row_dst.push_back(slot); }
@@ -1189,6 +1210,9 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     if (const char* v = std::getenv("SLLM_STREAM_SPLITS")) e->tune_stream_splits = std::min(std::max(0, std::atoi(v)), 8);
     e->pass_cap = opt.max_chunk_tokens ? (int)opt.max_chunk_tokens : 8192;
     e->pass_cap = std::max(e->pass_cap, e->max_batch);
+    e->chunk_tokens = e->pass_cap;
+    if (!opt.max_chunk_tokens && !e->f32) e->chunk_tokens = std::max(e->max_batch, pick_chunk_tokens(e->pass_cap, (int)D, (int)F, e->sm_count));
+    if (const char* v = std::getenv("SLLM_CHUNK_TOKENS")) e->chunk_tokens = std::min(e->pass_cap, std::max(e->max_batch, std::atoi(v)));
     e->logit_rows_cap = std::max(e->max_batch, 64);
 
     // registry: src/model.cpp:106-131
