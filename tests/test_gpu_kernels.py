@@ -130,6 +130,38 @@ def test_tensor_core_prefill_attention_full_context():
     assert out[-1] == int(np.argmax(want)) or (top2[1] - top2[0]) <= 2e-2 * np.abs(want).max()
 
 
+def test_wide_projection_tiles_in_all_their_variants(monkeypatch):
+    """A prefill chunk large enough for more projection tiles than SMs (4 x 2048 positions: 192 QKV and 352 gate/up
+    tiles of 128 x 256, 128 tiles of 128 x 128 for the two residual projections): the persistent tile loop with the
+    transposing epilogue (default), the same loop with the thread-per-row epilogue, and one tile per block, each
+    against the oracle on the last position of every sequence and on every position of one, and against each other."""
+    from tests.helpers import rel_err
+    cfg = Config(vocab=1024, context=2048, layers=2, d_model=256, heads=4, ffn=704)
+    prompts = [prompt_ids(60 + i, cfg.context, cfg.vocab) for i in range(4)]
+    got = {}
+    o = None
+    for name, var in (("default", None), ("thread-per-row", "SLLM_NO_WIDE_EPI"), ("one tile per block", "SLLM_NO_PERSISTENT_TC")):
+        if var:
+            monkeypatch.setenv(var, "1")
+        o, eng = make_pair(cfg, seed=12, stddev=0.05, fp32=False, max_batch=4, via_checkpoint=False, max_chunk_tokens=8192)
+        if var:
+            monkeypatch.delenv(var)
+        eng.prefill(prompts)
+        last = np.stack([eng.step_logits(i) for i in range(4)])
+        rows = eng.forward_logits(prompts[1], 1, cfg.context)[0]
+        got[name] = (last, rows)
+        del eng
+    ref_last = np.stack([o.forward(p, 1, p.size, row_from=p.size - 1)[0, -1] for p in prompts])
+    ref_rows = o.forward(prompts[1], 1, cfg.context)[0]
+    for name, (last, rows) in got.items():
+        assert np.isfinite(last).all() and np.isfinite(rows).all(), name
+        assert rel_err(last, ref_last) <= 2e-2, name
+        assert rel_err(rows, ref_rows) <= 2e-2, name
+    for name in ("thread-per-row", "one tile per block"):
+        assert rel_err(got[name][0], got["default"][0]) <= 1e-2, name
+        assert rel_err(got[name][1], got["default"][1]) <= 1e-2, name
+
+
 @pytest.mark.parametrize("fp32", [True, False])
 def test_attention_kernels_match_reference_op(fp32, golden_dir):
     """The decode attention kernels against the reference's own ops::attention (src/ops/attention.cpp:143-184): q, k, v
