@@ -337,13 +337,19 @@ __device__ int cand_solve(const float* w, int V, uint32_t lo, uint32_t hi, unsig
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     if (tid == 0) { cs.n = 0; cs.pick = kSampCand; }
     __syncthreads();
-    for (int i = tid; i < V; i += kSampThreads) {
-        const uint32_t k = __float_as_uint(w[i]);
+    auto take = [&](uint32_t k, int i) {
         if (k >= lo && k <= hi) {
             const int p = atomicAdd(&cs.n, 1);
             if (p < kSampCand) { cs.key[p] = k; cs.id[p] = i; }
         }
+    };
+    // 16 bytes per shared-memory load (the list's order does not matter: the candidates are ranked below)
+    const int V4 = V & ~3;
+    for (int i = tid * 4; i < V4; i += kSampThreads * 4) {
+        const uint4 k = *reinterpret_cast<const uint4*>(w + i);
+        take(k.x, i); take(k.y, i + 1); take(k.z, i + 2); take(k.w, i + 3);
     }
+    for (int i = V4 + tid; i < V; i += kSampThreads) take(__float_as_uint(w[i]), i);
     __syncthreads();
     const int n = min(cs.n, kSampCand);
     (void)n_expect;
