@@ -393,7 +393,7 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, T
     if (tc_smem_bytes(BN, 2, split) > e->max_dyn_smem) split = 1;
     const int kb_per_block = (nkb + split - 1) / split;
     // wide tiles without split-K: the transposing epilogue (16-byte accesses need every row count to be a multiple of 4)
-    const bool wide = BN >= 128 && split == 1 && a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
+    const bool wide = BN >= 64 && split == 1 && a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
     a.wide_epi = wide ? 1 : 0;
     const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split, wide)) / tc_stage_bytes(BN));
     a.split = split;

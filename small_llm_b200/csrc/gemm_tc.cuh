@@ -21,10 +21,10 @@ namespace sllm {
 
 constexpr int kTcBM = 128;          // weight rows per tile (UMMA M)
 constexpr int kTcBK = 64;           // K elements per stage = one 128-byte swizzle row of bf16
-// Epilogue warps: 8 (two per TMEM lane quarter) for narrow token tiles, 16 for wide ones, where the epilogue (loads
-// from L2 and stores scattered by token, a few per warp in flight) takes longer than the main loop: more warps keep
-// more of them in flight.
-template <int BN> __host__ __device__ constexpr int tc_epi_warps() { return BN >= 128 ? 16 : 8; }
+// Epilogue warps: 8 (two per TMEM lane quarter) for 32-token tiles, 16 from 64 tokens on, where the epilogue takes
+// longer than the main loop and the transposing form (TcArgs::wide_epi) needs groups of four warps per 16 columns
+// (measured at 256..512 sequences per decode pass: 0.3-0.8 % per iteration over 8 warps with the thread-per-row form).
+template <int BN> __host__ __device__ constexpr int tc_epi_warps() { return BN >= 64 ? 16 : 8; }
 template <int BN> __host__ __device__ constexpr int tc_threads() { return 64 + 32 * tc_epi_warps<BN>(); }
 constexpr int kTcMaxStages = 16;
 constexpr int kTcMaxSplit = 8;
