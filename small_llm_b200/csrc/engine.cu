@@ -142,7 +142,7 @@ struct sllm_engine {
     float* part_o = nullptr; float* part_ml = nullptr; unsigned int* ticket = nullptr;
     int split_tok_cap = 64;
     int tune_tc_split = 0;             // SLLM_TC_SPLIT: tuning aid, forces the split-K cluster size of the projections
-    int tune_no_wide_epi = 0;          // SLLM_NO_WIDE_EPI: wide projection tiles keep the thread-per-row epilogue (comparison aid)
+    int tune_no_wide_epi = 0;          // SLLM_NO_WIDE_EPI: the projections keep the thread-per-row epilogue (comparison aid, and the path of models whose row counts are not multiples of 4)
     int tune_no_persistent_tc = 0;     // SLLM_NO_PERSISTENT_TC: the wide projections run one tile per block (comparison aid)
     int tune_stream_splits = 0;        // SLLM_STREAM_SPLITS: tuning aid, overrides the split count of the streaming kernel
     unsigned long long* samp_mass = nullptr; unsigned int* samp_cnt = nullptr;   // sampler's level-0 histograms
@@ -390,10 +390,10 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, T
     // split-K over a cluster while the tiles alone leave most SMs idle: about 3 K blocks per block at least
     int split = std::min({kTcMaxSplit, std::max(1, nkb / 3), std::max(1, e->sm_count / tiles)});
     if (e->tune_tc_split > 0) split = std::min({e->tune_tc_split, kTcMaxSplit, nkb});
-    if (tc_smem_bytes(BN, 2, split) > e->max_dyn_smem) split = 1;
+    // the transposing epilogue (16-byte accesses need every row count to be a multiple of 4)
+    const bool wide = a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
+    if (tc_smem_bytes(BN, 2, split, wide) > e->max_dyn_smem) split = 1;
     const int kb_per_block = (nkb + split - 1) / split;
-    // wide tiles without split-K: the transposing epilogue (16-byte accesses need every row count to be a multiple of 4)
-    const bool wide = BN >= 64 && split == 1 && a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
     a.wide_epi = wide ? 1 : 0;
     const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split, wide)) / tc_stage_bytes(BN));
     a.split = split;

@@ -327,13 +327,15 @@ def test_eval_loss_matches_reference_cross_entropy(fp32, golden_dir):
         eng.eval_loss(ids, np.full(120, SMALL.vocab, np.int32), 3, 40)
 
 
-@pytest.mark.parametrize("split", [2, 4])
-def test_split_k_cluster_projections(split, monkeypatch):
+@pytest.mark.parametrize("split,epilogue", [(2, "transposing"), (4, "transposing"), (2, "thread-per-row"), (4, "thread-per-row")])
+def test_split_k_cluster_projections(split, epilogue, monkeypatch):
     """The tensor-core projections with their K blocks dealt over a thread-block cluster (forced here; the engine
-    chooses it by itself only when few tiles exist): same logits as the oracle within the bf16 tolerance, and the
-    same as the unsplit kernel up to the rounding of intermediate activations."""
+    chooses it by itself only when few tiles exist), with either epilogue: same logits as the oracle within the bf16
+    tolerance, and the same as the unsplit kernel up to the rounding of intermediate activations."""
     cfg = MID                                               # K = 128 (2 K blocks) and 200 (4, the last one ragged)
     ids = prompt_ids(1, 2 * 100, cfg.vocab)
+    if epilogue == "thread-per-row":
+        monkeypatch.setenv("SLLM_NO_WIDE_EPI", "1")
     monkeypatch.setenv("SLLM_TC_SPLIT", "1")
     o, eng1 = make_pair(cfg, seed=3, stddev=0.05, fp32=False, max_batch=2, via_checkpoint=False)
     base = eng1.forward_logits(ids, 2, 100)
