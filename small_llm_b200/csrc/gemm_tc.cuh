@@ -214,6 +214,10 @@ __global__ void __launch_bounds__(tc_threads<BN>()) k_gemm_tc(const __grid_const
     const int kb_first = (nkb_all * ks) / split;
     const int nkb = (nkb_all * (ks + 1)) / split - kb_first;                // this block's K blocks (>= 1)
 
+    if (threadIdx.x == 32) {                     // the descriptors' first use would otherwise wait for their fetch
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf0 + 8 * b, 1); mbar_init(acce0 + 8 * b, tc_epi_warps<BN>()); }
