@@ -383,16 +383,16 @@ int x_map(sllm_engine* e, const void* buf, uint64_t rows_cap, uint64_t K, int bn
     return SLLM_OK;
 }
 
+int pick_split(const sllm_engine* e, int bn, int tiles, int nkb, bool wide);
+
 template <int BN, int MODE>
 int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, bool pdl) {
     const int tiles = ((a.R + kTcBM - 1) / kTcBM) * ((a.n_tok + BN - 1) / BN);
     const int nkb = (a.K + kTcBK - 1) / kTcBK;
-    // split-K over a cluster while the tiles alone leave most SMs idle: about 3 K blocks per block at least
-    int split = std::min({kTcMaxSplit, std::max(1, nkb / 3), std::max(1, e->sm_count / tiles)});
-    if (e->tune_tc_split > 0) split = std::min({e->tune_tc_split, kTcMaxSplit, nkb});
     // the transposing epilogue (16-byte accesses need every row count to be a multiple of 4)
     const bool wide = a.R % 4 == 0 && a.m.D % 4 == 0 && a.m.hd % 4 == 0 && !e->tune_no_wide_epi;
-    if (tc_smem_bytes(BN, 2, split, wide) > e->max_dyn_smem) split = 1;
+    // split-K over a cluster while the tiles alone leave most SMs idle
+    const int split = pick_split(e, BN, tiles, nkb, wide);
     const int kb_per_block = (nkb + split - 1) / split;
     a.wide_epi = wide ? 1 : 0;
     const int fit = (int)((e->max_dyn_smem - tc_fixed_bytes(BN, split, wide)) / tc_stage_bytes(BN));
@@ -424,20 +424,39 @@ int launch_tc_bn(sllm_engine* e, const CUtensorMap& mw, const CUtensorMap& mx, T
     return SLLM_OK;
 }
 
+// split-K cluster size for `tiles` tiles of width bn over nkb K blocks: about 3 K blocks per block at least, no more
+// blocks than SMs, and the peers' accumulators must fit block 0's shared memory
+int pick_split(const sllm_engine* e, int bn, int tiles, int nkb, bool wide) {
+    int split = std::min({kTcMaxSplit, std::max(1, nkb / 3), std::max(1, e->sm_count / tiles)});
+    if (e->tune_tc_split > 0) split = std::min({e->tune_tc_split, kTcMaxSplit, nkb});
+    while (split > 1 && tc_smem_bytes(bn, 2, split, wide) > e->max_dyn_smem) --split;
+    return split;
+}
+
 // token-tile width: wide tiles for arithmetic intensity, narrower ones while the grid would not fill the GPU
-int pick_bn(const sllm_engine* e, int R, int n) {
+int pick_bn(const sllm_engine* e, int R, int n, int K) {
     const int tiles_m = (R + kTcBM - 1) / kTcBM;
     if (n <= 32) return 32;
     if (n <= 64) return tiles_m * 2 <= e->sm_count ? 32 : 64;      // small projections: two token tiles, twice the blocks
     // the widest token tile that still gives at least half an SM count of blocks: wide tiles re-read the
     // weight tile less often (shared-memory fill traffic from L2 is what bounds these small-K products)
     for (int bn : {256, 128, 64}) if (tiles_m * ((n + bn - 1) / bn) * 2 >= e->sm_count) return bn;
-    return 32;
+    // Few row tiles (the residual projections): a block of a 32-token tile takes in (128 + 32) x K x 2 bytes, and one
+    // SM's intake (~65 GB/s) is what its time is made of when K is large (the down projection: 553 KB).  64-token
+    // tiles with the K blocks dealt over a cluster move fewer bytes per SM; the hand-over between the cluster's blocks
+    // costs about as much as 100 KB of intake.  Taken when clearly ahead (measured: 4.19 -> 4.16 ms per iteration at
+    // 512 sequences, where the model says 0.58; 3.237 -> 3.247 at 384, where it says 0.71).
+    const int nkb = (K + kTcBK - 1) / kTcBK;
+    auto cost = [&](int bn) {
+        const int split = pick_split(e, bn, tiles_m * ((n + bn - 1) / bn), nkb, true);
+        return (double)(kTcBM + bn) * K * 2.0 / split + (split > 1 ? 100e3 : 0.0);
+    };
+    return cost(64) < 0.65 * cost(32) ? 64 : 32;
 }
 
 template <int MODE>
 int launch_tc(sllm_engine* e, const CUtensorMap& mw, const void* xbuf, uint64_t x_rows_cap, const TcArgs& a, bool pdl) {
-    const int bn = pick_bn(e, a.R, a.n_tok);
+    const int bn = pick_bn(e, a.R, a.n_tok, a.K);
     CUtensorMap mx;
     int rc = x_map(e, xbuf, x_rows_cap, (uint64_t)a.K, bn, &mx);
     if (rc) return rc;
