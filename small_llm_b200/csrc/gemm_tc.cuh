@@ -5,10 +5,13 @@
 //   out[tok][r] = sum_k X[tok][k] * W[r][k]        X: [tokens][K] bf16,  W: [R][K] bf16, both K-major
 //
 // The weight tile is the MMA's M side (128 rows = 128 TMEM lanes), the token tile its N side
-// (32..256 columns), so the batch does not have to fill a 128-row tile.  One thread block computes
-// one 128 x BN tile:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2.. (8 or 16 of them) =
-// epilogue (each reads 32 TMEM lanes of one half or quarter of the columns; thread = weight row, registers = tokens).  The same fused
-// epilogues as the GEMV family: RoPE + paged-KV append, residual add, SiLU(gate)*up, fp32 logits.
+// (32..256 columns), so the batch does not have to fill a 128-row tile.  A thread block computes 128 x BN tiles --
+// one, or, when there are more tiles than SMs, its share of them with two accumulators in tensor memory so that a
+// tile's epilogue overlaps the next tile's main loop:  warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2.. (8 or 16 of them) = epilogue.  The epilogue reads the accumulator as thread = weight row, registers =
+// tokens, and (row counts that are multiples of 4) transposes it through shared memory so that a lane stores 16 bytes
+// of consecutive rows of one token; the same fused epilogues as the GEMV family: RoPE + paged-KV append, residual
+// add, SiLU(gate)*up, fp32 logits.
 // Every mbarrier wait is bounded; on expiry the block raises the engine's status word, lets its
 // copies land, frees its tensor memory and returns.
 #pragma once
