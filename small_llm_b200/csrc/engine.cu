@@ -153,6 +153,12 @@ struct sllm_engine {
     double* d_draws = nullptr; size_t draws_cap = 0;
     // host pinned
     int* h_flags = nullptr;
+    // prefill chunk lists: two pinned staging buffers, so that the host builds chunk k + 1 while the GPU runs chunk k
+    // (a copy from pageable memory would first synchronise the stream)
+    unsigned char* h_pf[2] = {nullptr, nullptr};
+    cudaEvent_t ev_pf[2] = {nullptr, nullptr};
+    bool ev_pf_used[2] = {false, false};
+    int pf_next = 0;
 
     // graphs
     std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;   // exec + kernels per replay
@@ -1100,14 +1106,29 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
     auto flush = [&]() -> int {
         if (c_id.empty()) return SLLM_OK;
         const int n = (int)c_id.size();
-        CU(cudaMemcpyAsync(e->d_tok_id, c_id.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
-        CU(cudaMemcpyAsync(e->d_tok_slot, c_slot.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
-        CU(cudaMemcpyAsync(e->d_tok_pos, c_pos.data(), n * 4, cudaMemcpyHostToDevice, e->stream));
         // the attention grid takes its tiles in this order: the ones with the most KV pages first, so that the last
         // wave of blocks is the shortest
         std::stable_sort(c_tiles.begin(), c_tiles.end(),
                          [](const PfTile& x, const PfTile& y) { return x.pos0 + x.n_q > y.pos0 + y.n_q; });
-        CU(cudaMemcpyAsync(e->d_tiles, c_tiles.data(), c_tiles.size() * sizeof(PfTile), cudaMemcpyHostToDevice, e->stream));
+        // this chunk's lists go through one of two pinned buffers: [ids | slots | positions | row list | tiles]
+        const int b = e->pf_next;
+        e->pf_next ^= 1;
+        if (e->ev_pf_used[b]) CU(cudaEventSynchronize(e->ev_pf[b]));       // its previous contents have been copied
+        unsigned char* hp = e->h_pf[b];
+        uint32_t* h_id = reinterpret_cast<uint32_t*>(hp);
+        int* h_slot = reinterpret_cast<int*>(hp) + e->pass_cap;
+        int* h_pos = h_slot + e->pass_cap;
+        int* h_row = h_pos + e->pass_cap;
+        PfTile* h_tiles = reinterpret_cast<PfTile*>(h_row + e->pass_cap);
+        std::memcpy(h_id, c_id.data(), (size_t)n * 4);
+        std::memcpy(h_slot, c_slot.data(), (size_t)n * 4);
+        std::memcpy(h_pos, c_pos.data(), (size_t)n * 4);
+        std::memcpy(h_row, c_row.data(), c_row.size() * 4);
+        std::memcpy(h_tiles, c_tiles.data(), c_tiles.size() * sizeof(PfTile));
+        CU(cudaMemcpyAsync(e->d_tok_id, h_id, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+        CU(cudaMemcpyAsync(e->d_tok_slot, h_slot, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+        CU(cudaMemcpyAsync(e->d_tok_pos, h_pos, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+        CU(cudaMemcpyAsync(e->d_tiles, h_tiles, c_tiles.size() * sizeof(PfTile), cudaMemcpyHostToDevice, e->stream));
         PassView pv{e->d_tok_id, e->d_tok_slot, e->d_tok_pos, n, e->d_tiles, (int)c_tiles.size()};
         e->prefill_tokens += (uint64_t)n;
         int rc = run_pass(e, pv, nullptr, 0, nullptr, false);
@@ -1115,7 +1136,7 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
         // logits rows of this chunk, in groups that fit the logits buffer
         for (size_t r0 = 0; r0 < c_row.size(); r0 += e->logit_rows_cap) {
             const int nr = (int)std::min<size_t>(e->logit_rows_cap, c_row.size() - r0);
-            CU(cudaMemcpyAsync(e->d_row_tok, c_row.data() + r0, nr * 4, cudaMemcpyHostToDevice, e->stream));
+            CU(cudaMemcpyAsync(e->d_row_tok, h_row + r0, nr * 4, cudaMemcpyHostToDevice, e->stream));
             rc = run_head(e, pv, e->d_row_tok, nr, e->pass_logits);
             if (rc) return rc;
             if (h_targets) {
@@ -1132,8 +1153,11 @@ int prefill_impl(sllm_engine* e, const uint32_t* ids, const uint32_t* lens, uint
                     CU(cudaMemcpyAsync(e->step_logits + (size_t)c_row_dst[r0 + i] * m.V, e->pass_logits + (size_t)i * m.V,
                                        (size_t)m.V * 4, cudaMemcpyDeviceToDevice, e->stream));
             }
-            CU(cudaStreamSynchronize(e->stream));
+            // results for the host: the caller's buffers and the target list are reused per group
+            if (h_targets || host_logits) CU(cudaStreamSynchronize(e->stream));
         }
+        CU(cudaEventRecord(e->ev_pf[b], e->stream));             // every copy out of this staging buffer is enqueued before here
+        e->ev_pf_used[b] = true;
         row_base += c_row.size();
         c_id.clear(); c_slot.clear(); c_pos.clear(); c_row.clear(); c_row_dst.clear(); c_tiles.clear();
         return SLLM_OK;
@@ -1445,6 +1469,12 @@ int sllm_engine_create(const sllm_model_config* cfg, const sllm_engine_options* 
     A(&e->part_o, (size_t)e->split_tok_cap * H * kMaxSplits * hd, &e->scratch_bytes);
     A(&e->part_ml, (size_t)e->split_tok_cap * H * kMaxSplits * 2, &e->scratch_bytes);
     A(&e->ticket, (size_t)e->split_tok_cap * H, &e->scratch_bytes);
+    for (int b = 0; b < 2 && !rc; ++b) {
+        if (cudaMallocHost((void**)&e->h_pf[b], (size_t)e->pass_cap * (4 * sizeof(int) + sizeof(PfTile))) != cudaSuccess ||
+            cudaEventCreateWithFlags(&e->ev_pf[b], cudaEventDisableTiming) != cudaSuccess) {
+            e->err = "cudaMallocHost failed"; rc = SLLM_ERR_CUDA;
+        }
+    }
     if (!rc && cudaMallocHost((void**)&e->h_flags, (e->max_batch + 16) * sizeof(int)) != cudaSuccess) {
         e->err = "cudaMallocHost failed"; rc = SLLM_ERR_CUDA;
     }
@@ -1461,6 +1491,7 @@ void sllm_engine_destroy(sllm_engine* e) {
     for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.first);
     for (void* p : e->allocs) cudaFree(p);
     if (e->h_flags) cudaFreeHost(e->h_flags);
+    for (int b = 0; b < 2; ++b) { if (e->h_pf[b]) cudaFreeHost(e->h_pf[b]); if (e->ev_pf[b]) cudaEventDestroy(e->ev_pf[b]); }
     for (cudaEvent_t ev : e->step_events) cudaEventDestroy(ev);
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
