@@ -48,7 +48,8 @@ typedef struct {
                                   stream and accumulation.  SLLM_WEIGHTS_F32: fp32 weights and
                                   KV cache (parity runs that need the reference's streams)    */
     uint64_t kv_pages;         /* pages of 64 positions in the pool; 0 = max_batch * ceil(ctx/64) */
-    uint32_t max_chunk_tokens; /* tokens one prefill pass may carry; 0 = default (8192)       */
+    uint32_t max_chunk_tokens; /* tokens one prefill pass may carry; 0 = the engine chooses     */
+                               /* (at most 8192; bf16: where the projections' tiles fill the SMs) */
     int32_t device;            /* CUDA device ordinal; -1 = current                           */
     uint32_t use_graph;        /* replay the decode step as a CUDA graph (1) or launch (0)    */
     uint32_t reserved;
